@@ -1,0 +1,164 @@
+/*
+ * tvb.h — C ABI of the B200 (sm_100a) matmul path that stands in for
+ * Tensorvia's CUDA matmul operator and the device storage behind it.
+ *
+ * Every entry point is `extern "C"`, takes plain pointers and sizes, returns an
+ * int status (0 = TVB_OK), never throws and never exits the process.  A failed
+ * call leaves a message readable through tvb_last_error_string() (per thread).
+ *
+ * Data contract (the one Tensorvia's operator uses): dense, row-major,
+ * contiguous buffers.  2-D: A[M,K] @ B[K,N] -> C[M,N].  3-D: the leading
+ * dimension is a batch, A[b,M,K] @ B[b,K,N] -> C[b,M,N]; there is no
+ * broadcasting.  Element types are the eight Tensorvia dtypes, numbered as
+ * `via::DataType` numbers them (include/core/type_traits.h:123-132 of the
+ * reference).
+ */
+#ifndef TVB_H_
+#define TVB_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* via::DataType values, include/core/type_traits.h:123-132 */
+enum {
+  TVB_INT8 = 0,
+  TVB_INT16 = 1,
+  TVB_INT32 = 2,
+  TVB_INT64 = 3,
+  TVB_BFLOAT16 = 4,
+  TVB_FLOAT16 = 5,
+  TVB_FLOAT32 = 6,
+  TVB_FLOAT64 = 7
+};
+
+/* status codes */
+enum {
+  TVB_OK = 0,
+  TVB_ERR_INVALID_ARG = 1,   /* null pointer, bad device index, bad enum        */
+  TVB_ERR_SHAPE = 2,         /* a dimension <= 0 or beyond the supported range  */
+  TVB_ERR_DTYPE = 3,         /* dtype out of range, or dtC != compute_type      */
+  TVB_ERR_CUDA = 4,          /* a CUDA runtime / driver call failed             */
+  TVB_ERR_OOM = 5,           /* device or pinned-host allocation failed         */
+  TVB_ERR_NOT_INIT = 6,      /* tvb_init(dev) was not called for this device    */
+  TVB_ERR_KERNEL_TIMEOUT = 7,/* a bounded device-side wait ran out              */
+  TVB_ERR_NO_DEVICE = 8,     /* no CUDA device / not an sm_100 device           */
+  TVB_ERR_UNSUPPORTED = 9    /* forced algorithm cannot run this problem        */
+};
+
+/* kernel families; TVB_ALGO_AUTO picks per dtype and shape */
+enum {
+  TVB_ALGO_AUTO = 0,
+  TVB_ALGO_TCGEN05 = 1, /* TMA + tcgen05.mma + TMEM: f16, bf16, int8, and fp32 as 3xTF32 */
+  TVB_ALGO_SIMT = 2     /* CUDA-core register-tiled kernel: any of the 64 dtype pairs   */
+};
+
+/* distributions of tvb_fill_splitmix */
+enum {
+  TVB_DIST_UNIFORM_PM1 = 0, /* floats: uniform in [-1,1) with 24 random bits; ints: same as INT_PM10 */
+  TVB_DIST_INT_PM10 = 1     /* integers uniform in [-10,10]; floats get the integer value            */
+};
+
+typedef struct tvb_pool_stats {
+  uint64_t bytes_in_use;     /* handed out and not yet freed                       */
+  uint64_t bytes_cached;     /* held by the pool, free for reuse                   */
+  uint64_t backing_allocs;   /* times the pool went to cudaMalloc                  */
+  uint64_t backing_frees;    /* times the pool gave memory back with cudaFree      */
+  uint64_t reuse_hits;       /* allocations served from the cache                  */
+  uint64_t peak_bytes_in_use;
+} tvb_pool_stats;
+
+typedef struct tvb_plan_info {
+  int algo;                  /* TVB_ALGO_TCGEN05 or TVB_ALGO_SIMT                  */
+  int tile_m, tile_n, tile_k;/* CTA tile in elements (0 for SIMT tile_k)           */
+  int stages;                /* shared-memory pipeline depth                       */
+  int ctas;                  /* grid size                                          */
+  int passes;                /* tensor-core passes over K (3 for fp32 = 3xTF32)    */
+  uint64_t workspace_bytes;  /* scratch the call takes from the pool               */
+  uint64_t tiles;            /* output tiles over all batches                      */
+} tvb_plan_info;
+
+/* ---- lifetime -------------------------------------------------------------------
+ * Replaces the static CUDARegistrar + CUDAContext of the reference
+ * (src/init.cpp:18-34, include/backend/cuda/cuda_context.h:14-67): one context
+ * (stream, pool, status word) per device index instead of one global device. */
+int tvb_device_count(int* count);
+int tvb_init(int device);
+int tvb_shutdown(void);
+/* Blocks until the device's own stream is idle; returns TVB_ERR_KERNEL_TIMEOUT if
+ * a kernel recorded a wait that ran out (cuda_context.h:59-67 `wait()`). */
+int tvb_sync(int device);
+/* cudaStream_t of the device's context (ContextImpl::ctx_raw_ptr, include/core/context.h:3-7) */
+int tvb_stream(int device, void** stream);
+
+/* ---- storage ---------------------------------------------------------------------
+ * Replaces CUDATensor::init / FreeDeleter (include/backend/cuda/cuda_tensor.cpp:14-33,
+ * cuda_tensor.h:14-32: one cudaMalloc / cudaFree per tensor) with a caching pool;
+ * every block is 256-byte aligned, so it can back a TMA tensor map. */
+int tvb_malloc(int device, size_t bytes, void** ptr);
+int tvb_free(int device, void* ptr);
+int tvb_pool_get_stats(int device, tvb_pool_stats* out);
+int tvb_pool_trim(int device);             /* give cached blocks back to the driver */
+int tvb_host_alloc(size_t bytes, void** ptr); /* pinned host memory for staging      */
+int tvb_host_free(void* ptr);
+/* Copies (include/backend/cuda/cuda_copy.cpp:9-26).  `stream` NULL = the context's
+ * stream; the copy is asynchronous to the host when the host side is pinned. */
+int tvb_memcpy_h2d(int device, void* dst, const void* src, size_t bytes, void* stream);
+int tvb_memcpy_d2h(int device, void* dst, const void* src, size_t bytes, void* stream);
+int tvb_memcpy_d2d(int device, void* dst, const void* src, size_t bytes, void* stream);
+
+/* ---- dtype rules -----------------------------------------------------------------*/
+/* via::compute_type (include/core/type_traits.h:270-287); -1 for a bad dtype. */
+int tvb_compute_type(int dtype_a, int dtype_b);
+/* via::calc_dtype_size (include/core/type_traits.h:158-171); 0 for a bad dtype. */
+size_t tvb_dtype_size(int dtype);
+
+/* ---- the matmul operator ------------------------------------------------------------
+ * Replaces ops::MulImpl<Device::CUDA>::execute + mul_cuda_3d
+ * (src/backend/cuda/mul.cu:8-124).  A, B, C are device pointers on `device`;
+ * batch = 1 for the 2-D form.  dtype_c must equal tvb_compute_type(dtype_a,
+ * dtype_b).  The launch goes to `stream` (NULL = the context's stream) and
+ * returns without waiting; tvb_sync / a stream sync orders the result. */
+int tvb_matmul(int device, const void* A, const void* B, void* C,
+               int dtype_a, int dtype_b, int dtype_c,
+               int64_t batch, int64_t M, int64_t K, int64_t N, void* stream);
+/* Same, with the kernel family forced (tests and measurements). */
+int tvb_matmul_algo(int device, const void* A, const void* B, void* C,
+                    int dtype_a, int dtype_b, int dtype_c,
+                    int64_t batch, int64_t M, int64_t K, int64_t N, void* stream, int algo);
+/* What tvb_matmul would run for this problem. */
+int tvb_matmul_plan(int device, int dtype_a, int dtype_b,
+                    int64_t batch, int64_t M, int64_t K, int64_t N, int algo,
+                    tvb_plan_info* out);
+/* End-to-end form with HOST buffers: copies A and B in, multiplies, copies C out and
+ * waits.  This is what ops::Mul amounts to for a caller that holds host data
+ * (Tensor(void*, shape, dtype, device) + ops::Mul + to_host, src/tensor.cpp:96-117,
+ * 476-483).  Host buffers may be pageable or pinned (tvb_host_alloc). */
+int tvb_matmul_host(int device, const void* hA, const void* hB, void* hC,
+                    int dtype_a, int dtype_b, int dtype_c,
+                    int64_t batch, int64_t M, int64_t K, int64_t N);
+
+/* ---- helpers ------------------------------------------------------------------------*/
+/* Seeded, counter-based fill: element i = f(splitmix64(seed + i)).  Stands in for the
+ * time-seeded RandomImpl<CUDA> (src/backend/cuda/initializer.cu:99-124) so that any
+ * slice of a tensor can be regenerated on any device. */
+int tvb_fill_splitmix(int device, void* dst, int dtype, uint64_t count,
+                      uint64_t seed, uint64_t first_index, int dist, void* stream);
+/* Even split of `units` (rows or batches) in blocks of `granule` over `parts` ranks:
+ * the part `index` gets [*begin, *begin + *count). */
+int tvb_shard_range(int64_t units, int64_t granule, int parts, int index,
+                    int64_t* begin, int64_t* count);
+/* Number of kernels this library has launched since load (all devices). */
+uint64_t tvb_kernel_launches(void);
+/* Upper bound, in milliseconds, on any device-side wait (default 2000). */
+int tvb_set_wait_limit_ms(uint32_t ms);
+const char* tvb_last_error_string(void);
+const char* tvb_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TVB_H_ */

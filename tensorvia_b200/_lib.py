@@ -1,0 +1,98 @@
+"""ctypes binding of the C ABI in include/tvb.h.
+
+The library is loaded from the package's own `lib/` folder.  There is no fallback:
+if `libtvb.so` has not been built the import of this module raises, and every
+compute call goes to the CUDA kernels in that library or fails with the library's
+own error message.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "lib" / "libtvb.so"
+
+# via::DataType numbering (reference include/core/type_traits.h:123-132)
+INT8, INT16, INT32, INT64, BFLOAT16, FLOAT16, FLOAT32, FLOAT64 = range(8)
+DTYPE_NAMES = ["int8", "int16", "int32", "int64", "bfloat16", "float16", "float32", "float64"]
+
+ALGO_AUTO, ALGO_TCGEN05, ALGO_SIMT = 0, 1, 2
+DIST_UNIFORM_PM1, DIST_INT_PM10 = 0, 1
+
+OK = 0
+ERR_NAMES = {
+    1: "TVB_ERR_INVALID_ARG", 2: "TVB_ERR_SHAPE", 3: "TVB_ERR_DTYPE", 4: "TVB_ERR_CUDA",
+    5: "TVB_ERR_OOM", 6: "TVB_ERR_NOT_INIT", 7: "TVB_ERR_KERNEL_TIMEOUT", 8: "TVB_ERR_NO_DEVICE",
+    9: "TVB_ERR_UNSUPPORTED",
+}
+
+
+class PoolStats(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in (
+        "bytes_in_use", "bytes_cached", "backing_allocs", "backing_frees", "reuse_hits",
+        "peak_bytes_in_use")]
+
+
+class PlanInfo(C.Structure):
+    _fields_ = [("algo", C.c_int), ("tile_m", C.c_int), ("tile_n", C.c_int), ("tile_k", C.c_int),
+                ("stages", C.c_int), ("ctas", C.c_int), ("passes", C.c_int),
+                ("workspace_bytes", C.c_uint64), ("tiles", C.c_uint64)]
+
+
+class TvbError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"{ERR_NAMES.get(code, code)}: {message}")
+        self.code = code
+
+
+# Every symbol include/tvb.h declares, with its signature.
+_vp, _i, _i64, _u64, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_uint64, C.c_size_t
+SIGNATURES = {
+    "tvb_device_count": (_i, [C.POINTER(_i)]),
+    "tvb_init": (_i, [_i]),
+    "tvb_shutdown": (_i, []),
+    "tvb_sync": (_i, [_i]),
+    "tvb_stream": (_i, [_i, C.POINTER(_vp)]),
+    "tvb_malloc": (_i, [_i, _sz, C.POINTER(_vp)]),
+    "tvb_free": (_i, [_i, _vp]),
+    "tvb_pool_get_stats": (_i, [_i, C.POINTER(PoolStats)]),
+    "tvb_pool_trim": (_i, [_i]),
+    "tvb_host_alloc": (_i, [_sz, C.POINTER(_vp)]),
+    "tvb_host_free": (_i, [_vp]),
+    "tvb_memcpy_h2d": (_i, [_i, _vp, _vp, _sz, _vp]),
+    "tvb_memcpy_d2h": (_i, [_i, _vp, _vp, _sz, _vp]),
+    "tvb_memcpy_d2d": (_i, [_i, _vp, _vp, _sz, _vp]),
+    "tvb_compute_type": (_i, [_i, _i]),
+    "tvb_dtype_size": (_sz, [_i]),
+    "tvb_matmul": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _i64, _vp]),
+    "tvb_matmul_algo": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _i64, _vp, _i]),
+    "tvb_matmul_plan": (_i, [_i, _i, _i, _i64, _i64, _i64, _i64, _i, C.POINTER(PlanInfo)]),
+    "tvb_matmul_host": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _i64]),
+    "tvb_fill_splitmix": (_i, [_i, _vp, _i, _u64, _u64, _u64, _i, _vp]),
+    "tvb_shard_range": (_i, [_i64, _i64, _i, _i, C.POINTER(_i64), C.POINTER(_i64)]),
+    "tvb_kernel_launches": (_u64, []),
+    "tvb_set_wait_limit_ms": (_i, [C.c_uint32]),
+    "tvb_last_error_string": (C.c_char_p, []),
+    "tvb_version": (C.c_char_p, []),
+}
+
+
+def _load() -> C.CDLL:
+    if not LIB_PATH.exists():
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m tensorvia_b200.build` "
+            "(there is no CPU or PyTorch fallback for the matmul path)")
+    lib = C.CDLL(str(LIB_PATH))
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError here = header and library disagree
+        fn.restype = res
+        fn.argtypes = args
+    return lib
+
+
+lib = _load()
+
+
+def check(code: int) -> None:
+    if code != OK:
+        raise TvbError(code, lib.tvb_last_error_string().decode())

@@ -1,0 +1,95 @@
+"""Builds the native parts of the package in-tree with nvcc / g++.
+
+    python -m tensorvia_b200.build            # everything that is out of date
+    python -m tensorvia_b200.build --force
+
+Targets
+  lib/libtvb.so        CUDA kernels + the C ABI declared in include/tvb.h (sm_100a only)
+  lib/libtensorvia.so  C++ host layer: Tensor / ops::Mul / ops::matmul over the C ABI
+  lib/tv_mul_demo      the reference's tests/mul.cpp scenario written against that layer
+
+nvcc cross-compiles for sm_100a on a machine without a GPU.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+ROOT = PKG.parent
+CSRC = PKG / "csrc"
+CPP = PKG / "cpp"
+LIB = PKG / "lib"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC", "-shared", "-cudart", "static",
+]
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and Path(cand).exists():
+            return cand
+    raise RuntimeError("nvcc not found; the CUDA kernels cannot be built")
+
+
+def _stale(target: Path, sources) -> bool:
+    if not target.exists():
+        return True
+    t = target.stat().st_mtime
+    return any(Path(s).stat().st_mtime > t for s in sources)
+
+
+def _run(cmd) -> None:
+    proc = subprocess.run([str(c) for c in cmd], capture_output=True, text=True)
+    if proc.returncode != 0:
+        sys.stderr.write(proc.stdout + proc.stderr)
+        raise RuntimeError("build step failed: " + " ".join(str(c) for c in cmd))
+
+
+def build_libtvb(force: bool = False) -> Path:
+    target = LIB / "libtvb.so"
+    sources = sorted(CSRC.glob("*.cu")) + sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h"))
+    sources.append(ROOT / "include" / "tvb.h")
+    if force or _stale(target, sources):
+        LIB.mkdir(exist_ok=True)
+        _run([_nvcc(), *NVCC_FLAGS, f"-I{ROOT / 'include'}", f"-I{CSRC}",
+              *sorted(CSRC.glob("*.cu")), "-o", target])
+    return target
+
+
+def build_host_cpp(force: bool = False) -> Path | None:
+    """C++ Tensor/ops layer (g++ only; links libtvb.so)."""
+    if not CPP.exists():
+        return None
+    target = LIB / "libtensorvia.so"
+    srcs = sorted((CPP / "src").glob("*.cpp"))
+    hdrs = sorted((CPP / "include").rglob("*.h"))
+    cxx = shutil.which("g++") or "g++"
+    common = ["-std=gnu++20", "-O2", "-fPIC", f"-I{CPP / 'include'}", f"-I{CPP / 'include' / 'core'}",
+              f"-I{ROOT / 'include'}"]
+    if force or _stale(target, srcs + hdrs + [LIB / "libtvb.so"]):
+        _run([cxx, *common, "-shared", *srcs, f"-L{LIB}", "-ltvb", "-Wl,-rpath,$ORIGIN", "-o", target])
+    demo_src = CPP / "tests" / "mul.cpp"
+    demo = LIB / "tv_mul_demo"
+    if demo_src.exists() and (force or _stale(demo, [demo_src, target])):
+        _run([cxx, *common, demo_src, f"-L{LIB}", "-ltensorvia", "-ltvb", "-Wl,-rpath,$ORIGIN", "-o", demo])
+    api_src = CPP / "tests" / "api_check.cpp"
+    api = LIB / "tv_api_check"
+    if api_src.exists() and (force or _stale(api, [api_src, target])):
+        _run([cxx, *common, api_src, f"-L{LIB}", "-ltensorvia", "-ltvb", "-Wl,-rpath,$ORIGIN", "-o", api])
+    return target
+
+
+def build_all(force: bool = False) -> None:
+    build_libtvb(force)
+    build_host_cpp(force)
+
+
+if __name__ == "__main__":
+    build_all("--force" in sys.argv)
+    print("built:", ", ".join(sorted(p.name for p in LIB.iterdir())))

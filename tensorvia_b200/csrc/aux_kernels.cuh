@@ -1,0 +1,86 @@
+// Small HBM-bound helper kernels beside the GEMMs.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+namespace tvb {
+
+// ---- fp32 -> (hi, lo) TF32 split ----------------------------------------------------
+// hi = x rounded to TF32 (10 explicit mantissa bits), lo = (x - hi) rounded to TF32.
+// x - hi is exact in fp32, so hi + lo reproduces x to about 2^-22 relative and the
+// three products hi*hi + hi*lo + lo*hi recover an fp32-accurate product on the TF32
+// tensor cores.  Both outputs have their low 13 mantissa bits clear, so the result
+// does not depend on how the tensor core treats those bits.
+__device__ __forceinline__ float round_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+
+__global__ void __launch_bounds__(256)
+split_tf32_kernel(const float4* __restrict__ x, float4* __restrict__ hi, float4* __restrict__ lo,
+                  size_t n4, const float* __restrict__ xs, float* __restrict__ his,
+                  float* __restrict__ los, size_t n) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += stride) {
+    const float4 v = x[i];
+    float4 h, l;
+    h.x = round_tf32(v.x); l.x = round_tf32(v.x - h.x);
+    h.y = round_tf32(v.y); l.y = round_tf32(v.y - h.y);
+    h.z = round_tf32(v.z); l.z = round_tf32(v.z - h.z);
+    h.w = round_tf32(v.w); l.w = round_tf32(v.w - h.w);
+    hi[i] = h;
+    lo[i] = l;
+  }
+  // tail (n not a multiple of 4)
+  for (size_t i = n4 * 4 + static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += stride) {
+    const float v = xs[i];
+    const float h = round_tf32(v);
+    his[i] = h;
+    los[i] = round_tf32(v - h);
+  }
+}
+
+// ---- seeded counter-based fill --------------------------------------------------------
+// Element i takes the (first_index + i)-th output of SplitMix64 seeded with `seed`
+// (state_j = seed + (j+1) * 0x9E3779B97F4A7C15, then the standard finaliser).
+__host__ __device__ inline uint64_t splitmix64_at(uint64_t seed, uint64_t index) {
+  uint64_t z = seed + (index + 1ull) * 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+// uniform in [-1, 1) on a 2^-23 grid: exact in fp32
+__host__ __device__ inline float splitmix_pm1(uint64_t u) {
+  return static_cast<float>(static_cast<uint32_t>(u >> 40)) * (1.0f / 8388608.0f) - 1.0f;
+}
+// integer uniform in [-10, 10]
+__host__ __device__ inline int splitmix_pm10(uint64_t u) {
+  return static_cast<int>(u % 21ull) - 10;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+fill_splitmix_kernel(T* __restrict__ dst, size_t n, uint64_t seed, uint64_t first, int dist) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const uint64_t u = splitmix64_at(seed, first + i);
+    constexpr bool is_float = std::is_same_v<T, float> || std::is_same_v<T, double> ||
+                              std::is_same_v<T, __half> || std::is_same_v<T, __nv_bfloat16>;
+    if (is_float && dist == 0) {
+      const float f = splitmix_pm1(u);
+      if constexpr (std::is_same_v<T, __half>) dst[i] = __float2half_rn(f);
+      else if constexpr (std::is_same_v<T, __nv_bfloat16>) dst[i] = __float2bfloat16_rn(f);
+      else dst[i] = static_cast<T>(f);
+    } else {
+      const int v = splitmix_pm10(u);
+      if constexpr (std::is_same_v<T, __half>) dst[i] = __float2half_rn(static_cast<float>(v));
+      else if constexpr (std::is_same_v<T, __nv_bfloat16>) dst[i] = __float2bfloat16_rn(static_cast<float>(v));
+      else dst[i] = static_cast<T>(v);
+    }
+  }
+}
+
+}  // namespace tvb

@@ -1,0 +1,723 @@
+// C ABI of the sm_100a matmul path: contexts, storage pool, copies, kernel
+// selection and launch.  Declarations and the reference interfaces they replace
+// are in include/tvb.h.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cudaTypedefs.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <string>
+
+#include "aux_kernels.cuh"
+#include "block_pool.h"
+#include "simt_gemm.cuh"
+#include "tvb.h"
+#include "umma_gemm.cuh"
+
+namespace {
+
+using namespace tvb;
+
+constexpr int kMaxDevices = 64;
+
+thread_local std::string g_err;
+std::atomic<uint64_t> g_launches{0};
+std::atomic<uint32_t> g_wait_limit_ms{2000};
+
+int fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  g_err = buf;
+  return code;
+}
+
+#define TVB_CUDA(expr)                                                                      \
+  do {                                                                                      \
+    cudaError_t e__ = (expr);                                                               \
+    if (e__ != cudaSuccess) {                                                               \
+      const int code__ = (e__ == cudaErrorMemoryAllocation) ? TVB_ERR_OOM : TVB_ERR_CUDA;   \
+      return fail(code__, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e__), __FILE__, \
+                  __LINE__);                                                                \
+    }                                                                                       \
+  } while (0)
+
+struct Context {
+  int device = -1;
+  int sm_count = 0;
+  cudaStream_t stream = nullptr;
+  BlockPool* pool = nullptr;
+  uint32_t* d_status = nullptr;   // kernels OR timeout bits in here
+  uint32_t* h_status = nullptr;   // pinned copy read by tvb_sync
+  // grow-only scratch for the fp32 hi/lo split; `ws_event` orders its reuse across streams
+  void* ws = nullptr;
+  size_t ws_bytes = 0;
+  cudaEvent_t ws_event = nullptr;
+  bool ws_used = false;
+  std::mutex mu;
+};
+
+Context* g_ctx[kMaxDevices] = {};
+std::mutex g_mu;
+PFN_cuTensorMapEncodeTiled g_encode = nullptr;
+
+int backing_alloc(void** p, size_t bytes, void* user) {
+  Context* c = static_cast<Context*>(user);
+  int prev = -1;
+  cudaGetDevice(&prev);
+  if (prev != c->device) cudaSetDevice(c->device);
+  cudaError_t e = cudaMalloc(p, bytes);
+  if (e != cudaSuccess) cudaGetLastError();  // clear the sticky-free OOM so the retry is clean
+  if (prev >= 0 && prev != c->device) cudaSetDevice(prev);
+  return e == cudaSuccess ? 0 : 1;
+}
+int backing_free(void* p, void* user) {
+  Context* c = static_cast<Context*>(user);
+  int prev = -1;
+  cudaGetDevice(&prev);
+  if (prev != c->device) cudaSetDevice(c->device);
+  cudaError_t e = cudaFree(p);
+  if (prev >= 0 && prev != c->device) cudaSetDevice(prev);
+  return e == cudaSuccess ? 0 : 1;
+}
+
+int get_ctx(int device, Context** out) {
+  if (device < 0 || device >= kMaxDevices) return fail(TVB_ERR_INVALID_ARG, "device index %d out of range", device);
+  Context* c = g_ctx[device];
+  if (!c) return fail(TVB_ERR_NOT_INIT, "tvb_init(%d) has not been called", device);
+  *out = c;
+  return TVB_OK;
+}
+
+// Makes `device` current for the calling thread for the lifetime of the guard.
+struct DeviceGuard {
+  int prev = -1;
+  explicit DeviceGuard(int dev) {
+    cudaGetDevice(&prev);
+    if (prev != dev) cudaSetDevice(dev);
+    else prev = -1;
+  }
+  ~DeviceGuard() {
+    if (prev >= 0) cudaSetDevice(prev);
+  }
+};
+
+bool valid_dtype(int d) { return d >= 0 && d <= 7; }
+size_t dtype_size(int d) {
+  static const size_t s[8] = {1, 2, 4, 8, 2, 2, 4, 8};
+  return valid_dtype(d) ? s[d] : 0;
+}
+
+// ------------------------------------------------------------------------------------
+// tensor maps
+// ------------------------------------------------------------------------------------
+// 3-D map over a dense [batch, rows, cols] array (cols contiguous) with a
+// [1, box_rows, box_cols] box, 128-byte swizzle and zero fill outside the array.
+int make_map(CUtensorMap* map, CUtensorMapDataType type, size_t es, const void* base, uint64_t cols,
+             uint64_t rows, uint64_t batch, uint32_t box_cols, uint32_t box_rows) {
+  cuuint64_t dims[3] = {cols, rows, batch};
+  cuuint64_t strides[2] = {cols * es, rows * cols * es};
+  cuuint32_t box[3] = {box_cols, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = g_encode(map, type, 3, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(TVB_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled failed (%d) for [%llu,%llu,%llu] box [%u,%u]",
+                static_cast<int>(r), (unsigned long long)batch, (unsigned long long)rows,
+                (unsigned long long)cols, box_rows, box_cols);
+  return TVB_OK;
+}
+
+// ------------------------------------------------------------------------------------
+// SIMT dispatch: one instantiation per (A dtype, B dtype)
+// ------------------------------------------------------------------------------------
+using SimtLaunch = cudaError_t (*)(const void*, const void*, void*, int, int, int, int, cudaStream_t);
+
+template <int DA, int DB>
+cudaError_t launch_simt(const void* A, const void* B, void* C, int batch, int M, int N, int K,
+                        cudaStream_t s) {
+  using PT = PairTraits<DA, DB>;
+  const size_t sa = sizeof(typename PT::A), sb = sizeof(typename PT::B), sc = sizeof(typename PT::Out);
+  // gridDim.z carries the batch; it is limited to 65535, so long batches go in slices
+  for (int b0 = 0; b0 < batch; b0 += 65535) {
+    const int nb = (batch - b0 < 65535) ? batch - b0 : 65535;
+    dim3 grid((N + 63) / 64, (M + 63) / 64, nb);
+    simt_gemm_kernel<DA, DB><<<grid, 256, 0, s>>>(
+        static_cast<const char*>(A) + static_cast<size_t>(b0) * M * K * sa,
+        static_cast<const char*>(B) + static_cast<size_t>(b0) * K * N * sb,
+        static_cast<char*>(C) + static_cast<size_t>(b0) * M * N * sc, M, N, K);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+  }
+  return cudaSuccess;
+}
+
+#define TVB_SIMT_ROW(a)                                                                   \
+  {launch_simt<a, 0>, launch_simt<a, 1>, launch_simt<a, 2>, launch_simt<a, 3>,           \
+   launch_simt<a, 4>, launch_simt<a, 5>, launch_simt<a, 6>, launch_simt<a, 7>}
+const SimtLaunch g_simt[8][8] = {TVB_SIMT_ROW(0), TVB_SIMT_ROW(1), TVB_SIMT_ROW(2), TVB_SIMT_ROW(3),
+                                 TVB_SIMT_ROW(4), TVB_SIMT_ROW(5), TVB_SIMT_ROW(6), TVB_SIMT_ROW(7)};
+
+// ------------------------------------------------------------------------------------
+// tcgen05 dispatch
+// ------------------------------------------------------------------------------------
+struct UmmaPlan {
+  int op = -1;        // OP_*
+  int block_n = 256;
+  int stages = 4;
+  int passes = 1;
+  size_t es = 0;
+  CUtensorMapDataType tm_type = CU_TENSOR_MAP_DATA_TYPE_UINT8;
+};
+
+// Problems the tensor-core kernel takes: same-dtype f16 / bf16 / int8 / fp32 whose row
+// pitches (K and N elements) are whole multiples of 16 bytes (a TMA requirement).
+bool umma_eligible(int dta, int dtb, int64_t batch, int64_t M, int64_t K, int64_t N, const void* A,
+                   const void* B, const void* C, UmmaPlan* plan) {
+  if (dta != dtb) return false;
+  UmmaPlan p;
+  switch (dta) {
+    case TVB_FLOAT16: p.op = OP_F16; p.es = 2; p.tm_type = CU_TENSOR_MAP_DATA_TYPE_FLOAT16; break;
+    case TVB_BFLOAT16: p.op = OP_BF16; p.es = 2; p.tm_type = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16; break;
+    case TVB_INT8: p.op = OP_I8; p.es = 1; p.tm_type = CU_TENSOR_MAP_DATA_TYPE_UINT8; break;
+    case TVB_FLOAT32: p.op = OP_TF32; p.es = 4; p.tm_type = CU_TENSOR_MAP_DATA_TYPE_FLOAT32; p.passes = 3; break;
+    default: return false;
+  }
+  if ((K * p.es) % 16 != 0 || (N * p.es) % 16 != 0) return false;
+  if (M > 0x7FFFFFFFll || N > 0x7FFFFFFFll || K > 0x7FFFFFFFll || batch > 0x7FFFFFFFll) return false;
+  auto mis = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) != 0; };
+  if ((A && mis(A)) || (B && mis(B)) || (C && mis(C))) return false;
+  // Narrow outputs use 128-column tiles (less padding); everything else 256.
+  p.block_n = (N <= 128) ? 128 : 256;
+  if (const char* e = getenv("TVB_BLOCK_N")) {
+    const int v = atoi(e);
+    if (v == 128 || v == 256) p.block_n = v;
+  }
+  p.stages = (p.block_n == 256) ? 4 : 6;
+  const int64_t tiles = batch * ((M + 127) / 128) * ((N + p.block_n - 1) / p.block_n);
+  if (tiles > 0x7FFFFFFFll) return false;
+  *plan = p;
+  return true;
+}
+
+template <int OP, int BN, int ST>
+cudaError_t launch_umma_t(const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b0,
+                          const CUtensorMap& b1, const UmmaGemmParams& p, int grid, cudaStream_t s) {
+  using Cfg = UmmaGemmConfig<BN, ST>;
+  static std::atomic<bool> configured[kMaxDevices];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!configured[dev].load(std::memory_order_acquire)) {
+    cudaError_t e = cudaFuncSetAttribute(umma_gemm_kernel<OP, BN, ST>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    configured[dev].store(true, std::memory_order_release);
+  }
+  umma_gemm_kernel<OP, BN, ST><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, s>>>(a0, a1, b0, b1, p);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError();
+}
+
+template <int OP>
+cudaError_t launch_umma_op(int block_n, const CUtensorMap& a0, const CUtensorMap& a1,
+                           const CUtensorMap& b0, const CUtensorMap& b1, const UmmaGemmParams& p,
+                           int grid, cudaStream_t s) {
+  if (block_n == 256) return launch_umma_t<OP, 256, 4>(a0, a1, b0, b1, p, grid, s);
+  return launch_umma_t<OP, 128, 6>(a0, a1, b0, b1, p, grid, s);
+}
+
+int ensure_workspace(Context* c, size_t bytes, cudaStream_t s) {
+  if (c->ws_used) {
+    // the previous user of the scratch may still be running on another stream
+    TVB_CUDA(cudaStreamWaitEvent(s, c->ws_event, 0));
+  }
+  if (bytes <= c->ws_bytes) return TVB_OK;
+  if (c->ws) {
+    TVB_CUDA(cudaEventSynchronize(c->ws_event));
+    c->pool->release(c->ws);
+    c->ws = nullptr;
+    c->ws_bytes = 0;
+  }
+  void* p = nullptr;
+  if (c->pool->allocate(bytes, &p) != 0)
+    return fail(TVB_ERR_OOM, "out of device memory for %zu bytes of fp32 split scratch", bytes);
+  c->ws = p;
+  c->ws_bytes = BlockPool::round_size(bytes);
+  return TVB_OK;
+}
+
+int run_umma(Context* c, const UmmaPlan& plan, const void* A, const void* B, void* C, int64_t batch,
+             int64_t M, int64_t K, int64_t N, cudaStream_t s) {
+  const size_t es = plan.es;
+  const uint32_t bk = static_cast<uint32_t>(128 / es);
+  const uint32_t chunk_n = static_cast<uint32_t>(128 / es);
+  const void* a_hi = A;
+  const void* b_hi = B;
+  const void* a_lo = A;
+  const void* b_lo = B;
+
+  std::unique_lock<std::mutex> lock(c->mu, std::defer_lock);
+  if (plan.passes == 3) {
+    // fp32: split both operands into TF32 hi and lo parts in scratch memory
+    lock.lock();
+    const size_t na = static_cast<size_t>(batch) * M * K, nb = static_cast<size_t>(batch) * K * N;
+    const size_t na_b = (na * 4 + 255) / 256 * 256, nb_b = (nb * 4 + 255) / 256 * 256;
+    int rc = ensure_workspace(c, 2 * na_b + 2 * nb_b, s);
+    if (rc != TVB_OK) return rc;
+    char* w = static_cast<char*>(c->ws);
+    float* ahi = reinterpret_cast<float*>(w);
+    float* alo = reinterpret_cast<float*>(w + na_b);
+    float* bhi = reinterpret_cast<float*>(w + 2 * na_b);
+    float* blo = reinterpret_cast<float*>(w + 2 * na_b + nb_b);
+    auto split = [&](const void* src, float* hi, float* lo, size_t n) -> cudaError_t {
+      const size_t n4 = n / 4;
+      size_t blocks = (n4 + 255) / 256;
+      const size_t cap = static_cast<size_t>(c->sm_count) * 16;
+      if (blocks > cap) blocks = cap;
+      if (blocks == 0) blocks = 1;
+      split_tf32_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+          static_cast<const float4*>(src), reinterpret_cast<float4*>(hi), reinterpret_cast<float4*>(lo),
+          n4, static_cast<const float*>(src), hi, lo, n);
+      g_launches.fetch_add(1, std::memory_order_relaxed);
+      return cudaGetLastError();
+    };
+    TVB_CUDA(split(A, ahi, alo, na));
+    TVB_CUDA(split(B, bhi, blo, nb));
+    a_hi = ahi; a_lo = alo; b_hi = bhi; b_lo = blo;
+  }
+
+  CUtensorMap ma0, ma1, mb0, mb1;
+  int rc;
+  if ((rc = make_map(&ma0, plan.tm_type, es, a_hi, K, M, batch, bk, 128)) != TVB_OK) return rc;
+  if ((rc = make_map(&ma1, plan.tm_type, es, a_lo, K, M, batch, bk, 128)) != TVB_OK) return rc;
+  if ((rc = make_map(&mb0, plan.tm_type, es, b_hi, N, K, batch, chunk_n, bk)) != TVB_OK) return rc;
+  if ((rc = make_map(&mb1, plan.tm_type, es, b_lo, N, K, batch, chunk_n, bk)) != TVB_OK) return rc;
+
+  UmmaGemmParams p;
+  p.M = static_cast<int32_t>(M);
+  p.N = static_cast<int32_t>(N);
+  p.K = static_cast<int32_t>(K);
+  p.batch = static_cast<int32_t>(batch);
+  p.m_tiles = static_cast<int32_t>((M + 127) / 128);
+  p.n_tiles = static_cast<int32_t>((N + plan.block_n - 1) / plan.block_n);
+  p.k_blocks = static_cast<int32_t>((K + bk - 1) / bk);
+  p.passes = plan.passes;
+  p.total_tiles = static_cast<uint32_t>(batch * p.m_tiles * p.n_tiles);
+  p.C = C;
+  p.status = c->d_status;
+  p.wait_limit_ns = static_cast<uint64_t>(g_wait_limit_ms.load()) * 1000000ull;
+  const int grid = static_cast<int>(p.total_tiles < static_cast<uint32_t>(c->sm_count) ? p.total_tiles
+                                                                                       : c->sm_count);
+  cudaError_t e;
+  switch (plan.op) {
+    case OP_F16: e = launch_umma_op<OP_F16>(plan.block_n, ma0, ma1, mb0, mb1, p, grid, s); break;
+    case OP_BF16: e = launch_umma_op<OP_BF16>(plan.block_n, ma0, ma1, mb0, mb1, p, grid, s); break;
+    case OP_TF32: e = launch_umma_op<OP_TF32>(plan.block_n, ma0, ma1, mb0, mb1, p, grid, s); break;
+    default: e = launch_umma_op<OP_I8>(plan.block_n, ma0, ma1, mb0, mb1, p, grid, s); break;
+  }
+  if (e != cudaSuccess) return fail(TVB_ERR_CUDA, "tcgen05 GEMM launch failed: %s", cudaGetErrorString(e));
+  if (plan.passes == 3) {
+    TVB_CUDA(cudaEventRecord(c->ws_event, s));
+    c->ws_used = true;
+  }
+  return TVB_OK;
+}
+
+int validate_problem(const void* A, const void* B, const void* C, int dta, int dtb, int dtc,
+                     int64_t batch, int64_t M, int64_t K, int64_t N, bool need_ptrs) {
+  if (need_ptrs && (!A || !B || !C)) return fail(TVB_ERR_INVALID_ARG, "A, B and C must not be null");
+  if (!valid_dtype(dta) || !valid_dtype(dtb)) return fail(TVB_ERR_DTYPE, "dtype out of range: %d, %d", dta, dtb);
+  if (dtc != compute_type_of(dta, dtb))
+    return fail(TVB_ERR_DTYPE, "result dtype %d is not compute_type(%d,%d) = %d", dtc, dta, dtb,
+                compute_type_of(dta, dtb));
+  if (batch <= 0 || M <= 0 || K <= 0 || N <= 0)
+    return fail(TVB_ERR_SHAPE, "dimensions must be positive: batch=%lld M=%lld K=%lld N=%lld",
+                (long long)batch, (long long)M, (long long)K, (long long)N);
+  // the reference keeps its extents in `int` (mul.cu:53-56)
+  if (batch > 0x7FFFFFFFll || M > 0x7FFFFFFFll || K > 0x7FFFFFFFll || N > 0x7FFFFFFFll)
+    return fail(TVB_ERR_SHAPE, "a dimension exceeds 2^31-1");
+  if ((M + 63) / 64 > 65535) return fail(TVB_ERR_SHAPE, "M too large for the SIMT grid");
+  return TVB_OK;
+}
+
+int matmul_impl(int device, const void* A, const void* B, void* C, int dta, int dtb, int dtc,
+                int64_t batch, int64_t M, int64_t K, int64_t N, void* stream, int algo) {
+  Context* c = nullptr;
+  int rc = get_ctx(device, &c);
+  if (rc != TVB_OK) return rc;
+  rc = validate_problem(A, B, C, dta, dtb, dtc, batch, M, K, N, true);
+  if (rc != TVB_OK) return rc;
+  if (algo < TVB_ALGO_AUTO || algo > TVB_ALGO_SIMT) return fail(TVB_ERR_INVALID_ARG, "bad algo %d", algo);
+  DeviceGuard guard(device);
+  cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : c->stream;
+
+  UmmaPlan plan;
+  const bool can_umma = umma_eligible(dta, dtb, batch, M, K, N, A, B, C, &plan);
+  if (algo == TVB_ALGO_TCGEN05 && !can_umma)
+    return fail(TVB_ERR_UNSUPPORTED,
+                "tcgen05 path needs same-dtype f16/bf16/int8/fp32 operands, 16-byte aligned pointers "
+                "and K, N row pitches that are multiples of 16 bytes");
+  if (can_umma && algo != TVB_ALGO_SIMT) {
+    rc = run_umma(c, plan, A, B, C, batch, M, K, N, s);
+    if (rc == TVB_OK || algo == TVB_ALGO_TCGEN05 || rc != TVB_ERR_UNSUPPORTED) return rc;
+    // a tensor map the driver would not encode: fall through to the SIMT kernel
+  }
+  cudaError_t e = g_simt[dta][dtb](A, B, C, static_cast<int>(batch), static_cast<int>(M),
+                                   static_cast<int>(N), static_cast<int>(K), s);
+  if (e != cudaSuccess) return fail(TVB_ERR_CUDA, "SIMT GEMM launch failed: %s", cudaGetErrorString(e));
+  return TVB_OK;
+}
+
+template <typename T>
+cudaError_t launch_fill(void* dst, size_t n, uint64_t seed, uint64_t first, int dist, int sm_count,
+                        cudaStream_t s) {
+  size_t blocks = (n + 255) / 256;
+  const size_t cap = static_cast<size_t>(sm_count) * 16;
+  if (blocks > cap) blocks = cap;
+  if (blocks == 0) blocks = 1;
+  fill_splitmix_kernel<T><<<static_cast<unsigned>(blocks), 256, 0, s>>>(static_cast<T*>(dst), n, seed,
+                                                                        first, dist);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+// =====================================================================================
+// exported C ABI
+// =====================================================================================
+extern "C" {
+
+const char* tvb_last_error_string(void) { return g_err.c_str(); }
+const char* tvb_version(void) { return "tensorvia-b200 0.1 (sm_100a)"; }
+uint64_t tvb_kernel_launches(void) { return g_launches.load(); }
+
+int tvb_set_wait_limit_ms(uint32_t ms) {
+  if (ms == 0 || ms > 60000) return fail(TVB_ERR_INVALID_ARG, "wait limit must be 1..60000 ms");
+  g_wait_limit_ms.store(ms);
+  return TVB_OK;
+}
+
+int tvb_device_count(int* count) {
+  if (!count) return fail(TVB_ERR_INVALID_ARG, "count is null");
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    *count = 0;
+    return fail(TVB_ERR_NO_DEVICE, "cudaGetDeviceCount: %s", cudaGetErrorString(e));
+  }
+  *count = n;
+  return TVB_OK;
+}
+
+int tvb_init(int device) {
+  if (device < 0 || device >= kMaxDevices) return fail(TVB_ERR_INVALID_ARG, "device index %d out of range", device);
+  std::lock_guard<std::mutex> g(g_mu);
+  if (g_ctx[device]) return TVB_OK;
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) {
+    cudaGetLastError();
+    return fail(TVB_ERR_NO_DEVICE, "no CUDA device is visible");
+  }
+  if (device >= n) return fail(TVB_ERR_INVALID_ARG, "device %d requested but only %d visible", device, n);
+  cudaDeviceProp prop;
+  TVB_CUDA(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10)
+    return fail(TVB_ERR_NO_DEVICE, "device %d is sm_%d%d; this library only carries sm_100a code", device,
+                prop.major, prop.minor);
+  DeviceGuard guard(device);
+  if (!g_encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    TVB_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+    if (q != cudaDriverEntryPointSuccess || !fn)
+      return fail(TVB_ERR_CUDA, "driver does not export cuTensorMapEncodeTiled");
+    g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled>(fn);
+  }
+  Context* c = new Context();
+  c->device = device;
+  c->sm_count = prop.multiProcessorCount;
+  TVB_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+  TVB_CUDA(cudaEventCreateWithFlags(&c->ws_event, cudaEventDisableTiming));
+  TVB_CUDA(cudaMalloc(&c->d_status, sizeof(uint32_t)));
+  TVB_CUDA(cudaMemset(c->d_status, 0, sizeof(uint32_t)));
+  TVB_CUDA(cudaHostAlloc(&c->h_status, sizeof(uint32_t), cudaHostAllocDefault));
+  *c->h_status = 0;
+  c->pool = new BlockPool(backing_alloc, backing_free, c);
+  g_ctx[device] = c;
+  return TVB_OK;
+}
+
+int tvb_shutdown(void) {
+  std::lock_guard<std::mutex> g(g_mu);
+  for (int d = 0; d < kMaxDevices; ++d) {
+    Context* c = g_ctx[d];
+    if (!c) continue;
+    DeviceGuard guard(d);
+    cudaStreamSynchronize(c->stream);
+    if (c->ws) c->pool->release(c->ws);
+    delete c->pool;
+    cudaFree(c->d_status);
+    cudaFreeHost(c->h_status);
+    cudaEventDestroy(c->ws_event);
+    cudaStreamDestroy(c->stream);
+    delete c;
+    g_ctx[d] = nullptr;
+  }
+  return TVB_OK;
+}
+
+int tvb_stream(int device, void** stream) {
+  Context* c = nullptr;
+  int rc = get_ctx(device, &c);
+  if (rc != TVB_OK) return rc;
+  if (!stream) return fail(TVB_ERR_INVALID_ARG, "stream is null");
+  *stream = c->stream;
+  return TVB_OK;
+}
+
+int tvb_sync(int device) {
+  Context* c = nullptr;
+  int rc = get_ctx(device, &c);
+  if (rc != TVB_OK) return rc;
+  DeviceGuard guard(device);
+  TVB_CUDA(cudaMemcpyAsync(c->h_status, c->d_status, sizeof(uint32_t), cudaMemcpyDeviceToHost, c->stream));
+  TVB_CUDA(cudaStreamSynchronize(c->stream));
+  const uint32_t st = *c->h_status;
+  if (st != 0) {
+    cudaMemsetAsync(c->d_status, 0, sizeof(uint32_t), c->stream);
+    cudaStreamSynchronize(c->stream);
+    return fail(TVB_ERR_KERNEL_TIMEOUT,
+                "a device-side wait ran out (producer=%u mma=%u epilogue=%u); the result is invalid",
+                st & 1u, (st >> 1) & 1u, (st >> 2) & 1u);
+  }
+  return TVB_OK;
+}
+
+int tvb_malloc(int device, size_t bytes, void** ptr) {
+  Context* c = nullptr;
+  int rc = get_ctx(device, &c);
+  if (rc != TVB_OK) return rc;
+  if (!ptr) return fail(TVB_ERR_INVALID_ARG, "ptr is null");
+  if (bytes == 0) return fail(TVB_ERR_INVALID_ARG, "cannot allocate 0 bytes");
+  if (c->pool->allocate(bytes, ptr) != 0) {
+    *ptr = nullptr;
+    return fail(TVB_ERR_OOM, "out of device memory allocating %zu bytes on device %d", bytes, device);
+  }
+  return TVB_OK;
+}
+
+int tvb_free(int device, void* ptr) {
+  Context* c = nullptr;
+  int rc = get_ctx(device, &c);
+  if (rc != TVB_OK) return rc;
+  if (!ptr) return TVB_OK;
+  if (c->pool->release(ptr) != 0) return fail(TVB_ERR_INVALID_ARG, "pointer %p does not belong to the pool of device %d", ptr, device);
+  return TVB_OK;
+}
+
+int tvb_pool_get_stats(int device, tvb_pool_stats* out) {
+  Context* c = nullptr;
+  int rc = get_ctx(device, &c);
+  if (rc != TVB_OK) return rc;
+  if (!out) return fail(TVB_ERR_INVALID_ARG, "out is null");
+  const PoolStats s = c->pool->stats();
+  out->bytes_in_use = s.bytes_in_use;
+  out->bytes_cached = s.bytes_cached;
+  out->backing_allocs = s.backing_allocs;
+  out->backing_frees = s.backing_frees;
+  out->reuse_hits = s.reuse_hits;
+  out->peak_bytes_in_use = s.peak_bytes_in_use;
+  return TVB_OK;
+}
+
+int tvb_pool_trim(int device) {
+  Context* c = nullptr;
+  int rc = get_ctx(device, &c);
+  if (rc != TVB_OK) return rc;
+  DeviceGuard guard(device);
+  TVB_CUDA(cudaStreamSynchronize(c->stream));
+  c->pool->trim();
+  return TVB_OK;
+}
+
+int tvb_host_alloc(size_t bytes, void** ptr) {
+  if (!ptr || bytes == 0) return fail(TVB_ERR_INVALID_ARG, "bad arguments to tvb_host_alloc");
+  cudaError_t e = cudaHostAlloc(ptr, bytes, cudaHostAllocPortable);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    *ptr = nullptr;
+    return fail(TVB_ERR_OOM, "cudaHostAlloc(%zu) failed: %s", bytes, cudaGetErrorString(e));
+  }
+  return TVB_OK;
+}
+
+int tvb_host_free(void* ptr) {
+  if (!ptr) return TVB_OK;
+  TVB_CUDA(cudaFreeHost(ptr));
+  return TVB_OK;
+}
+
+static int copy_impl(int device, void* dst, const void* src, size_t bytes, void* stream, cudaMemcpyKind kind) {
+  Context* c = nullptr;
+  int rc = get_ctx(device, &c);
+  if (rc != TVB_OK) return rc;
+  if (!dst || !src) return fail(TVB_ERR_INVALID_ARG, "copy with a null pointer");
+  if (bytes == 0) return TVB_OK;
+  DeviceGuard guard(device);
+  cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : c->stream;
+  TVB_CUDA(cudaMemcpyAsync(dst, src, bytes, kind, s));
+  return TVB_OK;
+}
+int tvb_memcpy_h2d(int device, void* dst, const void* src, size_t bytes, void* stream) {
+  return copy_impl(device, dst, src, bytes, stream, cudaMemcpyHostToDevice);
+}
+int tvb_memcpy_d2h(int device, void* dst, const void* src, size_t bytes, void* stream) {
+  return copy_impl(device, dst, src, bytes, stream, cudaMemcpyDeviceToHost);
+}
+int tvb_memcpy_d2d(int device, void* dst, const void* src, size_t bytes, void* stream) {
+  return copy_impl(device, dst, src, bytes, stream, cudaMemcpyDeviceToDevice);
+}
+
+int tvb_compute_type(int a, int b) {
+  if (!valid_dtype(a) || !valid_dtype(b)) return -1;
+  return compute_type_of(a, b);
+}
+size_t tvb_dtype_size(int dtype) { return dtype_size(dtype); }
+
+int tvb_matmul(int device, const void* A, const void* B, void* C, int dta, int dtb, int dtc,
+               int64_t batch, int64_t M, int64_t K, int64_t N, void* stream) {
+  return matmul_impl(device, A, B, C, dta, dtb, dtc, batch, M, K, N, stream, TVB_ALGO_AUTO);
+}
+
+int tvb_matmul_algo(int device, const void* A, const void* B, void* C, int dta, int dtb, int dtc,
+                    int64_t batch, int64_t M, int64_t K, int64_t N, void* stream, int algo) {
+  return matmul_impl(device, A, B, C, dta, dtb, dtc, batch, M, K, N, stream, algo);
+}
+
+int tvb_matmul_plan(int device, int dta, int dtb, int64_t batch, int64_t M, int64_t K, int64_t N,
+                    int algo, tvb_plan_info* out) {
+  Context* c = nullptr;
+  int rc = get_ctx(device, &c);
+  if (rc != TVB_OK) return rc;
+  if (!out) return fail(TVB_ERR_INVALID_ARG, "out is null");
+  if (!valid_dtype(dta) || !valid_dtype(dtb)) return fail(TVB_ERR_DTYPE, "dtype out of range");
+  rc = validate_problem(nullptr, nullptr, nullptr, dta, dtb, compute_type_of(dta, dtb), batch, M, K, N, false);
+  if (rc != TVB_OK) return rc;
+  memset(out, 0, sizeof *out);
+  UmmaPlan plan;
+  const bool can = umma_eligible(dta, dtb, batch, M, K, N, nullptr, nullptr, nullptr, &plan);
+  if (algo == TVB_ALGO_TCGEN05 && !can) return fail(TVB_ERR_UNSUPPORTED, "problem is not eligible for the tcgen05 path");
+  if (can && algo != TVB_ALGO_SIMT) {
+    out->algo = TVB_ALGO_TCGEN05;
+    out->tile_m = 128;
+    out->tile_n = plan.block_n;
+    out->tile_k = static_cast<int>(128 / plan.es);
+    out->stages = plan.stages;
+    out->passes = plan.passes;
+    out->tiles = static_cast<uint64_t>(batch) * ((M + 127) / 128) * ((N + plan.block_n - 1) / plan.block_n);
+    out->ctas = static_cast<int>(out->tiles < static_cast<uint64_t>(c->sm_count) ? out->tiles : c->sm_count);
+    if (plan.passes == 3) {
+      const size_t na = static_cast<size_t>(batch) * M * K, nb = static_cast<size_t>(batch) * K * N;
+      out->workspace_bytes = 2 * ((na * 4 + 255) / 256 * 256) + 2 * ((nb * 4 + 255) / 256 * 256);
+    }
+  } else {
+    out->algo = TVB_ALGO_SIMT;
+    out->tile_m = 64;
+    out->tile_n = 64;
+    out->tile_k = 16;
+    out->stages = 1;
+    out->passes = 1;
+    out->tiles = static_cast<uint64_t>(batch) * ((M + 63) / 64) * ((N + 63) / 64);
+    out->ctas = static_cast<int>(out->tiles > 0x7FFFFFFF ? 0x7FFFFFFF : out->tiles);
+  }
+  return TVB_OK;
+}
+
+int tvb_matmul_host(int device, const void* hA, const void* hB, void* hC, int dta, int dtb, int dtc,
+                    int64_t batch, int64_t M, int64_t K, int64_t N) {
+  Context* c = nullptr;
+  int rc = get_ctx(device, &c);
+  if (rc != TVB_OK) return rc;
+  rc = validate_problem(hA, hB, hC, dta, dtb, dtc, batch, M, K, N, true);
+  if (rc != TVB_OK) return rc;
+  const size_t ba = static_cast<size_t>(batch) * M * K * dtype_size(dta);
+  const size_t bb = static_cast<size_t>(batch) * K * N * dtype_size(dtb);
+  const size_t bc = static_cast<size_t>(batch) * M * N * dtype_size(dtc);
+  void *dA = nullptr, *dB = nullptr, *dC = nullptr;
+  auto cleanup = [&]() {
+    if (dA) c->pool->release(dA);
+    if (dB) c->pool->release(dB);
+    if (dC) c->pool->release(dC);
+  };
+  if ((rc = tvb_malloc(device, ba, &dA)) != TVB_OK || (rc = tvb_malloc(device, bb, &dB)) != TVB_OK ||
+      (rc = tvb_malloc(device, bc, &dC)) != TVB_OK) {
+    cleanup();
+    return rc;
+  }
+  rc = tvb_memcpy_h2d(device, dA, hA, ba, nullptr);
+  if (rc == TVB_OK) rc = tvb_memcpy_h2d(device, dB, hB, bb, nullptr);
+  if (rc == TVB_OK) rc = matmul_impl(device, dA, dB, dC, dta, dtb, dtc, batch, M, K, N, nullptr, TVB_ALGO_AUTO);
+  if (rc == TVB_OK) rc = tvb_memcpy_d2h(device, hC, dC, bc, nullptr);
+  const int rs = tvb_sync(device);  // also drains the stream before the blocks go back to the pool
+  cleanup();
+  return rc != TVB_OK ? rc : rs;
+}
+
+int tvb_fill_splitmix(int device, void* dst, int dtype, uint64_t count, uint64_t seed,
+                      uint64_t first_index, int dist, void* stream) {
+  Context* c = nullptr;
+  int rc = get_ctx(device, &c);
+  if (rc != TVB_OK) return rc;
+  if (!dst) return fail(TVB_ERR_INVALID_ARG, "dst is null");
+  if (!valid_dtype(dtype)) return fail(TVB_ERR_DTYPE, "dtype out of range: %d", dtype);
+  if (dist != TVB_DIST_UNIFORM_PM1 && dist != TVB_DIST_INT_PM10) return fail(TVB_ERR_INVALID_ARG, "bad dist %d", dist);
+  if (count == 0) return TVB_OK;
+  DeviceGuard guard(device);
+  cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : c->stream;
+  cudaError_t e;
+  switch (dtype) {
+    case TVB_INT8: e = launch_fill<int8_t>(dst, count, seed, first_index, dist, c->sm_count, s); break;
+    case TVB_INT16: e = launch_fill<int16_t>(dst, count, seed, first_index, dist, c->sm_count, s); break;
+    case TVB_INT32: e = launch_fill<int32_t>(dst, count, seed, first_index, dist, c->sm_count, s); break;
+    case TVB_INT64: e = launch_fill<int64_t>(dst, count, seed, first_index, dist, c->sm_count, s); break;
+    case TVB_BFLOAT16: e = launch_fill<__nv_bfloat16>(dst, count, seed, first_index, dist, c->sm_count, s); break;
+    case TVB_FLOAT16: e = launch_fill<__half>(dst, count, seed, first_index, dist, c->sm_count, s); break;
+    case TVB_FLOAT32: e = launch_fill<float>(dst, count, seed, first_index, dist, c->sm_count, s); break;
+    default: e = launch_fill<double>(dst, count, seed, first_index, dist, c->sm_count, s); break;
+  }
+  if (e != cudaSuccess) return fail(TVB_ERR_CUDA, "fill launch failed: %s", cudaGetErrorString(e));
+  return TVB_OK;
+}
+
+int tvb_shard_range(int64_t units, int64_t granule, int parts, int index, int64_t* begin, int64_t* count) {
+  if (!begin || !count) return fail(TVB_ERR_INVALID_ARG, "begin/count is null");
+  if (units < 0 || granule <= 0 || parts <= 0 || index < 0 || index >= parts)
+    return fail(TVB_ERR_INVALID_ARG, "bad shard request: units=%lld granule=%lld parts=%d index=%d",
+                (long long)units, (long long)granule, parts, index);
+  // blocks of `granule` units are dealt out as evenly as possible; the first
+  // (blocks % parts) parts get one block more; the last block may be short
+  const int64_t blocks = (units + granule - 1) / granule;
+  const int64_t base = blocks / parts, extra = blocks % parts;
+  const int64_t first_block = index * base + (index < extra ? index : extra);
+  const int64_t nblocks = base + (index < extra ? 1 : 0);
+  int64_t b = first_block * granule;
+  int64_t e = (first_block + nblocks) * granule;
+  if (b > units) b = units;
+  if (e > units) e = units;
+  *begin = b;
+  *count = e - b;
+  return TVB_OK;
+}
+
+}  // extern "C"

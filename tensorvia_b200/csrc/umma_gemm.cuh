@@ -1,0 +1,360 @@
+// Persistent, warp-specialised tcgen05 GEMM for sm_100a.
+//
+//   C[b, M, N] = A[b, M, K] @ B[b, K, N]      (all dense row-major)
+//
+// replaces the 16x16 shared-memory CUDA-core kernel mul_cuda_3d of the reference
+// (src/backend/cuda/mul.cu:8-48) for the operand types the tensor cores take:
+// f16 x f16 -> f16, bf16 x bf16 -> bf16 (fp32 accumulate, round-to-nearest-even
+// on output, as `static_cast<S>(sum)` does there), int8 x int8 -> int8 (s32
+// accumulate, low byte kept, mul.cu:19,46) and fp32 as three TF32 passes over
+// pre-split operands.
+//
+// Layout of one CTA (192 threads, one CTA per SM, grid = min(tiles, SMs)):
+//   warp 0      TMA producer: A tile [128 rows x 128 B of K] (K-major, 128-B swizzle)
+//               and B tile [128 B of K-rows.. x BLOCK_N] as BLOCK_N*ES/128 boxes of
+//               [K-rows x 128 B of N] (MN-major, 128-B swizzle) into a STAGES-deep ring
+//   warp 1      allocates TMEM, issues tcgen05.mma (one lane), commits to mbarriers
+//   warps 2-5   epilogue: tcgen05.ld of the fp32/s32 accumulator, convert, store C
+// Two accumulators of BLOCK_N columns live in TMEM, so the epilogue of tile i
+// overlaps the main loop of tile i+1.
+//
+// B is consumed as stored ([K,N], N contiguous) through the MN-major operand mode:
+// nothing is transposed or repacked in HBM.
+//
+// Edges: TMA zero-fills out-of-range rows/columns of A and B (3-D tensor maps,
+// the batch is the outermost coordinate, so a tile never reads the next batch),
+// and stores are predicated on row < M, column < N.
+//
+// Every mbarrier wait is bounded (see ptx::mbar_wait).  A wait that runs out ORs a
+// code into *status, and every role then leaves its loop; TMEM is always freed.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "ptx_sm100.cuh"
+
+namespace tvb {
+
+enum : int { OP_F16 = 0, OP_BF16 = 1, OP_TF32 = 2, OP_I8 = 3 };
+
+template <int OP>
+struct OpTraits;
+template <>
+struct OpTraits<OP_F16> {
+  static constexpr int ES = 2, MMA = ptx::MMA_F16;
+  static constexpr uint32_t AB_FMT = 0, D_FMT = 1;
+  using Out = __half;
+};
+template <>
+struct OpTraits<OP_BF16> {
+  static constexpr int ES = 2, MMA = ptx::MMA_F16;
+  static constexpr uint32_t AB_FMT = 1, D_FMT = 1;
+  using Out = __nv_bfloat16;
+};
+template <>
+struct OpTraits<OP_TF32> {
+  static constexpr int ES = 4, MMA = ptx::MMA_TF32;
+  static constexpr uint32_t AB_FMT = 2, D_FMT = 1;
+  using Out = float;
+};
+template <>
+struct OpTraits<OP_I8> {
+  static constexpr int ES = 1, MMA = ptx::MMA_I8;
+  static constexpr uint32_t AB_FMT = 1, D_FMT = 2;
+  using Out = int8_t;
+};
+
+// status bits a kernel can set
+enum : uint32_t {
+  ST_PRODUCER_TIMEOUT = 1u,
+  ST_MMA_TIMEOUT = 2u,
+  ST_EPILOGUE_TIMEOUT = 4u,
+};
+
+struct UmmaGemmParams {
+  int32_t M, N, K, batch;
+  int32_t m_tiles, n_tiles, k_blocks;
+  int32_t passes;        // 1, or 3 when fp32 runs as (A_lo,B_hi), (A_hi,B_lo), (A_hi,B_hi)
+  uint32_t total_tiles;  // batch * m_tiles * n_tiles
+  void* C;
+  uint32_t* status;
+  uint64_t wait_limit_ns;
+};
+
+template <int BLOCK_N, int STAGES>
+struct UmmaGemmConfig {
+  static constexpr int BLOCK_M = 128;
+  static constexpr int A_BYTES = BLOCK_M * 128;
+  static constexpr int B_BYTES = BLOCK_N * 128;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int NUM_BARRIERS = 2 * STAGES + 4;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + NUM_BARRIERS * 8 + 16 + 1024;
+  static constexpr int TMEM_COLS = 2 * BLOCK_N;
+  static constexpr int THREADS = 192;
+};
+
+__device__ __forceinline__ void decode_tile(uint32_t tile, const UmmaGemmParams& p, int& b, int& mt,
+                                            int& nt) {
+  // Groups of 8 tile-rows are walked column by column, so the CTAs that run at the
+  // same time share a short band of A and a short band of B in L2.
+  const uint32_t per_batch = static_cast<uint32_t>(p.m_tiles) * static_cast<uint32_t>(p.n_tiles);
+  const uint32_t bb = tile / per_batch;
+  const uint32_t r = tile - bb * per_batch;
+  constexpr uint32_t GROUP = 8;
+  const uint32_t group_sz = GROUP * static_cast<uint32_t>(p.n_tiles);
+  const uint32_t g = r / group_sz;
+  const uint32_t first_m = g * GROUP;
+  const uint32_t gm = min(static_cast<uint32_t>(p.m_tiles) - first_m, GROUP);
+  const uint32_t rr = r - g * group_sz;
+  b = static_cast<int>(bb);
+  mt = static_cast<int>(first_m + rr % gm);
+  nt = static_cast<int>(rr / gm);
+}
+
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t pack_bf2(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// Converts 32 accumulator words of one output row and stores those left of column N.
+// N is a multiple of the 16-byte vector width of the output type (the launcher
+// guarantees it), so a vector is either wholly inside or wholly outside.
+template <int OP>
+__device__ __forceinline__ void store_row_chunk(typename OpTraits<OP>::Out* dst,
+                                                const uint32_t (&v)[32], int cols_left) {
+  uint4* d4 = reinterpret_cast<uint4*>(dst);
+  if constexpr (OP == OP_TF32) {
+#pragma unroll
+    for (int g = 0; g < 8; ++g)
+      if (g * 4 < cols_left) d4[g] = make_uint4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+  } else if constexpr (OP == OP_F16) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g)
+      if (g * 8 < cols_left)
+        d4[g] = make_uint4(pack_h2(__uint_as_float(v[8 * g]), __uint_as_float(v[8 * g + 1])),
+                           pack_h2(__uint_as_float(v[8 * g + 2]), __uint_as_float(v[8 * g + 3])),
+                           pack_h2(__uint_as_float(v[8 * g + 4]), __uint_as_float(v[8 * g + 5])),
+                           pack_h2(__uint_as_float(v[8 * g + 6]), __uint_as_float(v[8 * g + 7])));
+  } else if constexpr (OP == OP_BF16) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g)
+      if (g * 8 < cols_left)
+        d4[g] = make_uint4(pack_bf2(__uint_as_float(v[8 * g]), __uint_as_float(v[8 * g + 1])),
+                           pack_bf2(__uint_as_float(v[8 * g + 2]), __uint_as_float(v[8 * g + 3])),
+                           pack_bf2(__uint_as_float(v[8 * g + 4]), __uint_as_float(v[8 * g + 5])),
+                           pack_bf2(__uint_as_float(v[8 * g + 6]), __uint_as_float(v[8 * g + 7])));
+  } else {
+    // int8: keep the low byte of each s32 sum (two's-complement wrap)
+#pragma unroll
+    for (int g = 0; g < 2; ++g)
+      if (g * 16 < cols_left) {
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int i = 16 * g + 4 * j;
+          w[j] = (v[i] & 0xFFu) | ((v[i + 1] & 0xFFu) << 8) | ((v[i + 2] & 0xFFu) << 16) |
+                 ((v[i + 3] & 0xFFu) << 24);
+        }
+        d4[g] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+  }
+}
+
+template <int OP, int BLOCK_N, int STAGES>
+__global__ void __launch_bounds__(192, 1)
+umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
+                 const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
+                 const UmmaGemmParams p) {
+  using T = OpTraits<OP>;
+  using Cfg = UmmaGemmConfig<BLOCK_N, STAGES>;
+  using Out = typename T::Out;
+  constexpr int ES = T::ES;
+  constexpr int BLOCK_M = Cfg::BLOCK_M;
+  constexpr int BK = 128 / ES;                  // K elements per stage
+  constexpr int CHUNK_N = 128 / ES;             // N elements per 128-byte B box
+  constexpr int NCHUNK = BLOCK_N / CHUNK_N;     // B boxes per stage
+  constexpr int CHUNK_BYTES = BK * 128;         // bytes of one B box = LBO of the B descriptor
+  constexpr int KSTEPS = 4;                     // 128 B of K per stage / 32 B per MMA
+  constexpr int B_KSTEP_BYTES = (32 / ES) * 128;// K rows of one MMA x 128 B
+  constexpr uint32_t IDESC = ptx::make_instr_desc(T::D_FMT, T::AB_FMT, 0u, 1u, BLOCK_M, BLOCK_N);
+  static_assert(BLOCK_N % 16 == 0 && BLOCK_N >= 32 && BLOCK_N <= 256, "UMMA N range");
+  static_assert((Cfg::TMEM_COLS & (Cfg::TMEM_COLS - 1)) == 0 && Cfg::TMEM_COLS >= 32, "TMEM cols");
+  static_assert(BLOCK_N % CHUNK_N == 0, "B tile must be whole 128-byte boxes");
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
+  const uint32_t bar_base = base + STAGES * Cfg::STAGE_BYTES;
+  auto a_smem = [&](int s) { return base + s * Cfg::STAGE_BYTES; };
+  auto b_smem = [&](int s) { return base + s * Cfg::STAGE_BYTES + Cfg::A_BYTES; };
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
+  auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
+  const uint32_t slot_addr = bar_base + 8u * Cfg::NUM_BARRIERS;
+  volatile uint32_t* slot_ptr =
+      reinterpret_cast<volatile uint32_t*>(smem_raw + (slot_addr - raw_addr));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(tfull_bar(b), 1);
+      ptx::mbar_init(tempty_bar(b), 128);
+    }
+    ptx::fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    ptx::prefetch_tmap(&tmA0);
+    ptx::prefetch_tmap(&tmB0);
+    if (p.passes > 1) {
+      ptx::prefetch_tmap(&tmA1);
+      ptx::prefetch_tmap(&tmB1);
+    }
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(slot_addr, Cfg::TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *slot_ptr;
+
+  const int k_iters = p.k_blocks * p.passes;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (uint32_t tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
+        int b, mt, nt;
+        decode_tile(tile, p, b, mt, nt);
+        for (int kb = 0; ok && kb < p.k_blocks; ++kb) {
+          for (int pass = 0; pass < p.passes; ++pass) {
+            if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, p.wait_limit_ns)) {
+              atomicOr(p.status, ST_PRODUCER_TIMEOUT);
+              ok = false;
+              break;
+            }
+            // pass order with 3 passes: (A_lo,B_hi), (A_hi,B_lo), (A_hi,B_hi)
+            const CUtensorMap* ma = (p.passes > 1 && pass == 0) ? &tmA1 : &tmA0;
+            const CUtensorMap* mb = (p.passes > 1 && pass == 1) ? &tmB1 : &tmB0;
+            ptx::mbar_expect_tx(full_bar(stage), Cfg::STAGE_BYTES);
+            ptx::tma_load_3d(a_smem(stage), ma, full_bar(stage), kb * BK, mt * BLOCK_M, b);
+#pragma unroll
+            for (int c = 0; c < NCHUNK; ++c)
+              ptx::tma_load_3d(b_smem(stage) + c * CHUNK_BYTES, mb, full_bar(stage),
+                               nt * BLOCK_N + c * CHUNK_N, kb * BK, b);
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t local = 0;
+      bool ok = true;
+      for (uint32_t tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x, ++local) {
+        const uint32_t buf = local & 1u;
+        const uint32_t acc_phase = (local >> 1) & 1u;
+        if (!ptx::mbar_wait(tempty_bar(buf), acc_phase ^ 1u, p.wait_limit_ns)) {
+          atomicOr(p.status, ST_MMA_TIMEOUT);
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BLOCK_N;
+        for (int it = 0; it < k_iters; ++it) {
+          if (!ptx::mbar_wait(full_bar(stage), phase, p.wait_limit_ns)) {
+            atomicOr(p.status, ST_MMA_TIMEOUT);
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t a0 = a_smem(stage);
+          const uint32_t b0 = b_smem(stage);
+#pragma unroll
+          for (int k = 0; k < KSTEPS; ++k) {
+            const uint64_t adesc = ptx::make_smem_desc(a0 + k * 32, 16, 1024);
+            const uint64_t bdesc = ptx::make_smem_desc(b0 + k * B_KSTEP_BYTES, CHUNK_BYTES, 1024);
+            ptx::tc_mma<T::MMA>(d_tmem, adesc, bdesc, IDESC, (it > 0 || k > 0) ? 1u : 0u);
+          }
+          ptx::tc_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) ptx::tc_commit(tfull_bar(buf));  // accumulator complete
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int quad = warp & 3;  // a warp may only read TMEM lanes 32*(warp%4) .. +31
+    uint32_t local = 0;
+    bool ok = true;
+    Out* const Cbase = reinterpret_cast<Out*>(p.C);
+    for (uint32_t tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x, ++local) {
+      int b, mt, nt;
+      decode_tile(tile, p, b, mt, nt);
+      const uint32_t buf = local & 1u;
+      const uint32_t acc_phase = (local >> 1) & 1u;
+      // the verdict is made warp-uniform: tcgen05.ld below needs all 32 lanes
+      const bool landed = ptx::mbar_wait(tfull_bar(buf), acc_phase, p.wait_limit_ns);
+      if (!__all_sync(0xffffffffu, landed)) {
+        if (lane == 0) atomicOr(p.status, ST_EPILOGUE_TIMEOUT);
+        ok = false;
+        break;
+      }
+      ptx::tc_fence_after();
+      const int row = mt * BLOCK_M + quad * 32 + lane;
+      const int col0 = nt * BLOCK_N;
+      const uint32_t taddr = tmem_base + buf * BLOCK_N + (static_cast<uint32_t>(quad * 32) << 16);
+      Out* crow = Cbase + (static_cast<size_t>(b) * p.M + static_cast<size_t>(row)) * p.N + col0;
+#pragma unroll 1
+      for (int c = 0; c < BLOCK_N / 32; ++c) {
+        uint32_t v[32];
+        ptx::tmem_ld_32x32(taddr + c * 32, v);
+        ptx::tmem_ld_wait();
+        const int cols_left = p.N - (col0 + c * 32);
+        if (row < p.M && cols_left > 0) store_row_chunk<OP>(crow + c * 32, v, cols_left);
+      }
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(tempty_bar(buf));
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    // Loads that were issued but never consumed (only after a timeout) land within
+    // microseconds; give them a bounded moment before the CTA's shared memory goes away.
+    if (*reinterpret_cast<volatile uint32_t*>(p.status) != 0) {
+      const uint64_t t0 = ptx::globaltimer_ns();
+      while (ptx::globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+}  // namespace tvb

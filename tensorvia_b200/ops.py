@@ -1,0 +1,151 @@
+"""Python face of the matmul operator, for tests, the benchmark and torch users.
+
+It mirrors the reference's `ops::Mul(const Tensor&, const Tensor&)` front end
+(src/ops.cpp:540-573): the same shape rules, the same failures (as RuntimeError,
+where the reference throws std::runtime_error), the result dtype of
+`via::compute_type` (include/core/type_traits.h:270-287) — and then hands dense
+row-major device buffers to the C ABI (`tvb_matmul`).  torch supplies device
+memory and streams only; no torch kernel runs on this path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from ._lib import (ALGO_AUTO, ALGO_SIMT, ALGO_TCGEN05, BFLOAT16, FLOAT16, FLOAT32, FLOAT64, INT8,
+                   INT16, INT32, INT64, check, lib)
+
+_initialised: set[int] = set()
+
+
+def init(device: int = 0) -> None:
+    """Creates the library's context (stream, pool, status word) for `device`."""
+    if device not in _initialised:
+        check(lib.tvb_init(device))
+        _initialised.add(device)
+
+
+def compute_type(dtype_a: int, dtype_b: int) -> int:
+    r = lib.tvb_compute_type(dtype_a, dtype_b)
+    if r < 0:
+        raise RuntimeError("Unsupported DataType")
+    return r
+
+
+def dtype_size(dtype: int) -> int:
+    return int(lib.tvb_dtype_size(dtype))
+
+
+def _torch_maps():
+    import torch
+    to_tvb = {torch.int8: INT8, torch.int16: INT16, torch.int32: INT32, torch.int64: INT64,
+              torch.bfloat16: BFLOAT16, torch.float16: FLOAT16, torch.float32: FLOAT32,
+              torch.float64: FLOAT64}
+    from_tvb = {v: k for k, v in to_tvb.items()}
+    return to_tvb, from_tvb
+
+
+def check_shapes(shape_a, shape_b) -> tuple[int, int, int, int]:
+    """The validity rules of ops::Mul (src/ops.cpp:544-556). Returns (batch, M, K, N)."""
+    if len(shape_a) != len(shape_b):
+        raise RuntimeError(
+            f"Tensors a and b must have the same rank,but got {len(shape_a)} and {len(shape_b)}")
+    if len(shape_a) not in (2, 3):
+        raise RuntimeError(f"Tensors a and b dims must be 2 or 3,but got {len(shape_a)}")
+    if len(shape_a) == 3:
+        if shape_a[0] != shape_b[0]:
+            raise RuntimeError("Tensors a and b must have the same batch size")
+        if shape_a[2] != shape_b[1]:
+            raise RuntimeError(f"Tensors common dim must match,but {shape_a[2]} and {shape_b[1]}")
+        return int(shape_a[0]), int(shape_a[1]), int(shape_a[2]), int(shape_b[2])
+    if shape_a[1] != shape_b[0]:
+        raise RuntimeError(f"Tensors common dim must match,but {shape_a[1]} and {shape_b[0]}")
+    return 1, int(shape_a[0]), int(shape_a[1]), int(shape_b[1])
+
+
+def matmul(a, b, *, algo: int = ALGO_AUTO, out=None):
+    """C = A @ B for torch CUDA tensors (2-D, or 3-D with a leading batch).
+
+    Runs on torch's current stream of the tensors' device and does not wait.
+    Inputs must be contiguous: the reference reads its operands as dense row-major
+    whatever their strides (src/backend/cuda/mul.cu:96-121), so a strided view is
+    rejected here instead of being multiplied as if it were dense.
+    """
+    import torch
+    to_tvb, from_tvb = _torch_maps()
+    if a.device != b.device:
+        raise RuntimeError("Tensors a and b device mismatch!")
+    if a.device.type != "cuda":
+        raise RuntimeError("tensorvia_b200.matmul needs CUDA tensors; there is no CPU path")
+    batch, M, K, N = check_shapes(tuple(a.shape), tuple(b.shape))
+    if not a.is_contiguous() or not b.is_contiguous():
+        raise RuntimeError("matmul operands must be contiguous row-major")
+    dta, dtb = to_tvb[a.dtype], to_tvb[b.dtype]
+    dtc = compute_type(dta, dtb)
+    dev = a.device.index if a.device.index is not None else torch.cuda.current_device()
+    init(dev)
+    shape_c = (batch, M, N) if a.dim() == 3 else (M, N)
+    if out is None:
+        out = torch.empty(shape_c, dtype=from_tvb[dtc], device=a.device)
+    else:
+        if tuple(out.shape) != shape_c or out.dtype != from_tvb[dtc] or not out.is_contiguous():
+            raise RuntimeError("out has the wrong shape, dtype or layout")
+    stream = torch.cuda.current_stream(a.device).cuda_stream
+    check(lib.tvb_matmul_algo(dev, a.data_ptr(), b.data_ptr(), out.data_ptr(), dta, dtb, dtc,
+                              batch, M, K, N, C.c_void_p(stream), algo))
+    return out
+
+
+Mul = matmul  # the name the reference source uses (include/core/ops.h:59)
+
+_NP_DTYPES = {INT8: np.int8, INT16: np.int16, INT32: np.int32, INT64: np.int64,
+              BFLOAT16: np.uint16, FLOAT16: np.float16, FLOAT32: np.float32, FLOAT64: np.float64}
+
+
+def np_dtype(dtype: int):
+    """numpy storage type of a Tensorvia dtype (bfloat16 travels as raw uint16 bits)."""
+    return _NP_DTYPES[dtype]
+
+
+def matmul_host(a: np.ndarray, b: np.ndarray, dtype_a: int, dtype_b: int, device: int = 0) -> np.ndarray:
+    """End-to-end call with host arrays: copy in, multiply on the GPU, copy out, wait.
+
+    `a` and `b` hold the raw element bits in the numpy type `np_dtype` gives.
+    """
+    batch, M, K, N = check_shapes(a.shape, b.shape)
+    if a.dtype != np_dtype(dtype_a) or b.dtype != np_dtype(dtype_b):
+        raise RuntimeError("array storage type does not match the stated dtype")
+    a = np.ascontiguousarray(a)
+    b = np.ascontiguousarray(b)
+    dtc = compute_type(dtype_a, dtype_b)
+    shape_c = (batch, M, N) if a.ndim == 3 else (M, N)
+    c = np.empty(shape_c, dtype=np_dtype(dtc))
+    init(device)
+    check(lib.tvb_matmul_host(device, a.ctypes.data, b.ctypes.data, c.ctypes.data, dtype_a, dtype_b,
+                              dtc, batch, M, K, N))
+    return c
+
+
+def plan(dtype_a: int, dtype_b: int, batch: int, M: int, K: int, N: int, algo: int = ALGO_AUTO,
+         device: int = 0) -> _lib.PlanInfo:
+    init(device)
+    info = _lib.PlanInfo()
+    check(lib.tvb_matmul_plan(device, dtype_a, dtype_b, batch, M, K, N, algo, C.byref(info)))
+    return info
+
+
+def sync(device: int = 0) -> None:
+    """Waits for the library's own stream and raises if a kernel reported a timed-out wait."""
+    check(lib.tvb_sync(device))
+
+
+def shard_range(units: int, granule: int, parts: int, index: int) -> tuple[int, int]:
+    begin, count = C.c_int64(), C.c_int64()
+    check(lib.tvb_shard_range(units, granule, parts, index, C.byref(begin), C.byref(count)))
+    return begin.value, count.value
+
+
+def kernel_launches() -> int:
+    return int(lib.tvb_kernel_launches())
