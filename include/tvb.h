@@ -56,6 +56,12 @@ enum {
   TVB_ALGO_SIMT = 2     /* CUDA-core register-tiled kernel: any of the 64 dtype pairs   */
 };
 
+/* how fp32 x fp32 runs on the tensor cores */
+enum {
+  TVB_FP32_3XTF32 = 0, /* hi/lo split, three TF32 passes: fp32-grade accuracy (default)  */
+  TVB_FP32_1XTF32 = 1  /* one TF32 pass on the raw operands: ~1e-3 relative error        */
+};
+
 /* distributions of tvb_fill_splitmix */
 enum {
   TVB_DIST_UNIFORM_PM1 = 0, /* floats: uniform in [-1,1) with 24 random bits; ints: same as INT_PM10 */
@@ -151,6 +157,12 @@ int tvb_fill_splitmix(int device, void* dst, int dtype, uint64_t count,
  * the part `index` gets [*begin, *begin + *count). */
 int tvb_shard_range(int64_t units, int64_t granule, int parts, int index,
                     int64_t* begin, int64_t* count);
+/* Process-wide choice of the fp32 tensor-core scheme (TVB_FP32_*).  The reference
+ * accumulates fp32 products in fp32 (mul.cu:19); only TVB_FP32_3XTF32 meets that. */
+int tvb_set_fp32_mode(int mode);
+/* The split the fp32 path applies to its operands: hi = tf32(x), lo = tf32(x - hi),
+ * `count` floats each; all three pointers 16-byte aligned device memory. */
+int tvb_split_tf32(int device, const void* src, void* hi, void* lo, uint64_t count, void* stream);
 /* Number of kernels this library has launched since load (all devices). */
 uint64_t tvb_kernel_launches(void);
 /* Upper bound, in milliseconds, on any device-side wait (default 2000). */

@@ -18,6 +18,7 @@ DTYPE_NAMES = ["int8", "int16", "int32", "int64", "bfloat16", "float16", "float3
 
 ALGO_AUTO, ALGO_TCGEN05, ALGO_SIMT = 0, 1, 2
 DIST_UNIFORM_PM1, DIST_INT_PM10 = 0, 1
+FP32_3XTF32, FP32_1XTF32 = 0, 1
 
 OK = 0
 ERR_NAMES = {
@@ -70,6 +71,8 @@ SIGNATURES = {
     "tvb_matmul_host": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _i64]),
     "tvb_fill_splitmix": (_i, [_i, _vp, _i, _u64, _u64, _u64, _i, _vp]),
     "tvb_shard_range": (_i, [_i64, _i64, _i, _i, C.POINTER(_i64), C.POINTER(_i64)]),
+    "tvb_set_fp32_mode": (_i, [_i]),
+    "tvb_split_tf32": (_i, [_i, _vp, _vp, _vp, _u64, _vp]),
     "tvb_kernel_launches": (_u64, []),
     "tvb_set_wait_limit_ms": (_i, [C.c_uint32]),
     "tvb_last_error_string": (C.c_char_p, []),

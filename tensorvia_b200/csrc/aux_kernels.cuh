@@ -43,6 +43,41 @@ split_tf32_kernel(const float4* __restrict__ x, float4* __restrict__ hi, float4*
   }
 }
 
+// Same split for the B operand, written transposed: src is [batch][K][N], hi and lo are
+// [batch][N][K], so the tensor core can read B K-major.  32x32 tiles go through shared
+// memory: reads are coalesced along N, writes along K.  grid = (ceil(N/32), ceil(K/32), batch).
+__global__ void __launch_bounds__(256)
+split_tf32_transpose_kernel(const float* __restrict__ src, float* __restrict__ hi,
+                            float* __restrict__ lo, int K, int N) {
+  __shared__ float th[32][33];
+  __shared__ float tl[32][33];
+  const size_t boff = static_cast<size_t>(blockIdx.z) * K * N;
+  const int n0 = blockIdx.x * 32, k0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int k = k0 + ty + 8 * j, n = n0 + tx;
+    float h = 0.f, l = 0.f;
+    if (k < K && n < N) {
+      const float v = src[boff + static_cast<size_t>(k) * N + n];
+      h = round_tf32(v);
+      l = round_tf32(v - h);
+    }
+    th[ty + 8 * j][tx] = h;
+    tl[ty + 8 * j][tx] = l;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int n = n0 + ty + 8 * j, k = k0 + tx;
+    if (n < N && k < K) {
+      const size_t o = boff + static_cast<size_t>(n) * K + k;
+      hi[o] = th[tx][ty + 8 * j];
+      lo[o] = tl[tx][ty + 8 * j];
+    }
+  }
+}
+
 // ---- seeded counter-based fill --------------------------------------------------------
 // Element i takes the (first_index + i)-th output of SplitMix64 seeded with `seed`
 // (state_j = seed + (j+1) * 0x9E3779B97F4A7C15, then the standard finaliser).

@@ -28,6 +28,7 @@ constexpr int kMaxDevices = 64;
 thread_local std::string g_err;
 std::atomic<uint64_t> g_launches{0};
 std::atomic<uint32_t> g_wait_limit_ms{2000};
+std::atomic<int> g_fp32_mode{TVB_FP32_3XTF32};
 
 int fail(int code, const char* fmt, ...) {
   char buf[512];
@@ -189,10 +190,14 @@ bool umma_eligible(int dta, int dtb, int64_t batch, int64_t M, int64_t K, int64_
     case TVB_FLOAT16: p.op = OP_F16; p.es = 2; p.tm_type = CU_TENSOR_MAP_DATA_TYPE_FLOAT16; break;
     case TVB_BFLOAT16: p.op = OP_BF16; p.es = 2; p.tm_type = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16; break;
     case TVB_INT8: p.op = OP_I8; p.es = 1; p.tm_type = CU_TENSOR_MAP_DATA_TYPE_UINT8; break;
-    case TVB_FLOAT32: p.op = OP_TF32; p.es = 4; p.tm_type = CU_TENSOR_MAP_DATA_TYPE_FLOAT32; p.passes = 3; break;
+    case TVB_FLOAT32:
+      p.op = OP_TF32; p.es = 4; p.tm_type = CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+      p.passes = (g_fp32_mode.load() == TVB_FP32_1XTF32) ? 1 : 3;
+      break;
     default: return false;
   }
   if ((K * p.es) % 16 != 0 || (N * p.es) % 16 != 0) return false;
+  if (p.op == OP_TF32 && (K + 31) / 32 > 65535) return false;  // grid.y of the transposing split
   if (M > 0x7FFFFFFFll || N > 0x7FFFFFFFll || K > 0x7FFFFFFFll || batch > 0x7FFFFFFFll) return false;
   auto mis = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) != 0; };
   if ((A && mis(A)) || (B && mis(B)) || (C && mis(C))) return false;
@@ -212,7 +217,7 @@ bool umma_eligible(int dta, int dtb, int64_t batch, int64_t M, int64_t K, int64_
 template <int OP, int BN, int ST>
 cudaError_t launch_umma_t(const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b0,
                           const CUtensorMap& b1, const UmmaGemmParams& p, int grid, cudaStream_t s) {
-  using Cfg = UmmaGemmConfig<BN, ST>;
+  using Cfg = UmmaGemmConfig<OP, BN, ST>;
   static std::atomic<bool> configured[kMaxDevices];
   int dev = 0;
   cudaGetDevice(&dev);
@@ -233,6 +238,19 @@ cudaError_t launch_umma_op(int block_n, const CUtensorMap& a0, const CUtensorMap
                            int grid, cudaStream_t s) {
   if (block_n == 256) return launch_umma_t<OP, 256, 4>(a0, a1, b0, b1, p, grid, s);
   return launch_umma_t<OP, 128, 6>(a0, a1, b0, b1, p, grid, s);
+}
+
+cudaError_t launch_split(Context* c, const void* src, float* hi, float* lo, size_t n, cudaStream_t s) {
+  const size_t n4 = n / 4;
+  size_t blocks = (n4 + 255) / 256;
+  const size_t cap = static_cast<size_t>(c->sm_count) * 16;
+  if (blocks > cap) blocks = cap;
+  if (blocks == 0) blocks = 1;
+  split_tf32_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+      static_cast<const float4*>(src), reinterpret_cast<float4*>(hi), reinterpret_cast<float4*>(lo), n4,
+      static_cast<const float*>(src), hi, lo, n);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError();
 }
 
 int ensure_workspace(Context* c, size_t bytes, cudaStream_t s) {
@@ -266,8 +284,9 @@ int run_umma(Context* c, const UmmaPlan& plan, const void* A, const void* B, voi
   const void* b_lo = B;
 
   std::unique_lock<std::mutex> lock(c->mu, std::defer_lock);
-  if (plan.passes == 3) {
+  if (plan.op == OP_TF32) {
     // fp32: split both operands into TF32 hi and lo parts in scratch memory
+    // (B transposed on the way); the 1xTF32 mode uses the hi parts only
     lock.lock();
     const size_t na = static_cast<size_t>(batch) * M * K, nb = static_cast<size_t>(batch) * K * N;
     const size_t na_b = (na * 4 + 255) / 256 * 256, nb_b = (nb * 4 + 255) / 256 * 256;
@@ -278,20 +297,20 @@ int run_umma(Context* c, const UmmaPlan& plan, const void* A, const void* B, voi
     float* alo = reinterpret_cast<float*>(w + na_b);
     float* bhi = reinterpret_cast<float*>(w + 2 * na_b);
     float* blo = reinterpret_cast<float*>(w + 2 * na_b + nb_b);
-    auto split = [&](const void* src, float* hi, float* lo, size_t n) -> cudaError_t {
-      const size_t n4 = n / 4;
-      size_t blocks = (n4 + 255) / 256;
-      const size_t cap = static_cast<size_t>(c->sm_count) * 16;
-      if (blocks > cap) blocks = cap;
-      if (blocks == 0) blocks = 1;
-      split_tf32_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(
-          static_cast<const float4*>(src), reinterpret_cast<float4*>(hi), reinterpret_cast<float4*>(lo),
-          n4, static_cast<const float*>(src), hi, lo, n);
-      g_launches.fetch_add(1, std::memory_order_relaxed);
-      return cudaGetLastError();
-    };
-    TVB_CUDA(split(A, ahi, alo, na));
-    TVB_CUDA(split(B, bhi, blo, nb));
+    TVB_CUDA(launch_split(c, A, ahi, alo, na, s));
+    {
+      // B is split and transposed to [batch][N][K] in the same pass
+      for (int64_t b0 = 0; b0 < batch; b0 += 65535) {
+        const int nbz = static_cast<int>(batch - b0 < 65535 ? batch - b0 : 65535);
+        dim3 grid(static_cast<unsigned>((N + 31) / 32), static_cast<unsigned>((K + 31) / 32), nbz);
+        const size_t off = static_cast<size_t>(b0) * K * N;
+        split_tf32_transpose_kernel<<<grid, 256, 0, s>>>(static_cast<const float*>(B) + off, bhi + off,
+                                                          blo + off, static_cast<int>(K),
+                                                          static_cast<int>(N));
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        TVB_CUDA(cudaGetLastError());
+      }
+    }
     a_hi = ahi; a_lo = alo; b_hi = bhi; b_lo = blo;
   }
 
@@ -299,8 +318,14 @@ int run_umma(Context* c, const UmmaPlan& plan, const void* A, const void* B, voi
   int rc;
   if ((rc = make_map(&ma0, plan.tm_type, es, a_hi, K, M, batch, bk, 128)) != TVB_OK) return rc;
   if ((rc = make_map(&ma1, plan.tm_type, es, a_lo, K, M, batch, bk, 128)) != TVB_OK) return rc;
-  if ((rc = make_map(&mb0, plan.tm_type, es, b_hi, N, K, batch, chunk_n, bk)) != TVB_OK) return rc;
-  if ((rc = make_map(&mb1, plan.tm_type, es, b_lo, N, K, batch, chunk_n, bk)) != TVB_OK) return rc;
+  if (plan.op == OP_TF32) {
+    // B^T[batch][N][K]: boxes of block_n rows x 128 B of K
+    if ((rc = make_map(&mb0, plan.tm_type, es, b_hi, K, N, batch, bk, plan.block_n)) != TVB_OK) return rc;
+    if ((rc = make_map(&mb1, plan.tm_type, es, b_lo, K, N, batch, bk, plan.block_n)) != TVB_OK) return rc;
+  } else {
+    if ((rc = make_map(&mb0, plan.tm_type, es, b_hi, N, K, batch, chunk_n, bk)) != TVB_OK) return rc;
+    if ((rc = make_map(&mb1, plan.tm_type, es, b_lo, N, K, batch, chunk_n, bk)) != TVB_OK) return rc;
+  }
 
   UmmaGemmParams p;
   p.M = static_cast<int32_t>(M);
@@ -311,6 +336,12 @@ int run_umma(Context* c, const UmmaPlan& plan, const void* A, const void* B, voi
   p.n_tiles = static_cast<int32_t>((N + plan.block_n - 1) / plan.block_n);
   p.k_blocks = static_cast<int32_t>((K + bk - 1) / bk);
   p.passes = plan.passes;
+  // fp32: 8 stages = 256 elements of K per TMEM-resident partial sum (TVB_K_CHUNK overrides)
+  p.k_chunk_blocks = 8;
+  if (const char* e = getenv("TVB_K_CHUNK")) {
+    const int v = atoi(e);
+    if (v >= 1 && v <= 4096) p.k_chunk_blocks = v;
+  }
   p.total_tiles = static_cast<uint32_t>(batch * p.m_tiles * p.n_tiles);
   p.C = C;
   p.status = c->d_status;
@@ -325,7 +356,7 @@ int run_umma(Context* c, const UmmaPlan& plan, const void* A, const void* B, voi
     default: e = launch_umma_op<OP_I8>(plan.block_n, ma0, ma1, mb0, mb1, p, grid, s); break;
   }
   if (e != cudaSuccess) return fail(TVB_ERR_CUDA, "tcgen05 GEMM launch failed: %s", cudaGetErrorString(e));
-  if (plan.passes == 3) {
+  if (plan.op == OP_TF32) {
     TVB_CUDA(cudaEventRecord(c->ws_event, s));
     c->ws_used = true;
   }
@@ -404,6 +435,26 @@ uint64_t tvb_kernel_launches(void) { return g_launches.load(); }
 int tvb_set_wait_limit_ms(uint32_t ms) {
   if (ms == 0 || ms > 60000) return fail(TVB_ERR_INVALID_ARG, "wait limit must be 1..60000 ms");
   g_wait_limit_ms.store(ms);
+  return TVB_OK;
+}
+
+int tvb_set_fp32_mode(int mode) {
+  if (mode != TVB_FP32_3XTF32 && mode != TVB_FP32_1XTF32) return fail(TVB_ERR_INVALID_ARG, "bad fp32 mode %d", mode);
+  g_fp32_mode.store(mode);
+  return TVB_OK;
+}
+
+int tvb_split_tf32(int device, const void* src, void* hi, void* lo, uint64_t count, void* stream) {
+  Context* c = nullptr;
+  int rc = get_ctx(device, &c);
+  if (rc != TVB_OK) return rc;
+  if (!src || !hi || !lo) return fail(TVB_ERR_INVALID_ARG, "null pointer");
+  auto mis = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) != 0; };
+  if (mis(src) || mis(hi) || mis(lo)) return fail(TVB_ERR_INVALID_ARG, "pointers must be 16-byte aligned");
+  if (count == 0) return TVB_OK;
+  DeviceGuard guard(device);
+  cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : c->stream;
+  TVB_CUDA(launch_split(c, src, static_cast<float*>(hi), static_cast<float*>(lo), count, s));
   return TVB_OK;
 }
 
@@ -627,7 +678,7 @@ int tvb_matmul_plan(int device, int dta, int dtb, int64_t batch, int64_t M, int6
     out->passes = plan.passes;
     out->tiles = static_cast<uint64_t>(batch) * ((M + 127) / 128) * ((N + plan.block_n - 1) / plan.block_n);
     out->ctas = static_cast<int>(out->tiles < static_cast<uint64_t>(c->sm_count) ? out->tiles : c->sm_count);
-    if (plan.passes == 3) {
+    if (plan.op == OP_TF32) {
       const size_t na = static_cast<size_t>(batch) * M * K, nb = static_cast<size_t>(batch) * K * N;
       out->workspace_bytes = 2 * ((na * 4 + 255) / 256 * 256) + 2 * ((nb * 4 + 255) / 256 * 256);
     }

@@ -11,15 +11,17 @@
 //
 // Layout of one CTA (192 threads, one CTA per SM, grid = min(tiles, SMs)):
 //   warp 0      TMA producer: A tile [128 rows x 128 B of K] (K-major, 128-B swizzle)
-//               and B tile [128 B of K-rows.. x BLOCK_N] as BLOCK_N*ES/128 boxes of
-//               [K-rows x 128 B of N] (MN-major, 128-B swizzle) into a STAGES-deep ring
+//               and B tile [128 B worth of K rows x BLOCK_N] as BLOCK_N*ES/128 boxes of
+//               [K-rows x 128 B of N] (MN-major, 128-B swizzle) into a STAGES-deep ring;
+//               for fp32 the B operand is the pre-transposed B^T[N,K], loaded like A
 //   warp 1      allocates TMEM, issues tcgen05.mma (one lane), commits to mbarriers
 //   warps 2-5   epilogue: tcgen05.ld of the fp32/s32 accumulator, convert, store C
+//               (fp32: warps 2-9, which also sum the K chunks in registers)
 // Two accumulators of BLOCK_N columns live in TMEM, so the epilogue of tile i
 // overlaps the main loop of tile i+1.
 //
-// B is consumed as stored ([K,N], N contiguous) through the MN-major operand mode:
-// nothing is transposed or repacked in HBM.
+// f16, bf16 and int8 B is consumed as stored ([K,N], N contiguous) through the MN-major
+// operand mode: nothing is transposed or repacked in HBM.
 //
 // Edges: TMA zero-fills out-of-range rows/columns of A and B (3-D tensor maps,
 // the batch is the outermost coordinate, so a tile never reads the next batch),
@@ -42,25 +44,29 @@ struct OpTraits;
 template <>
 struct OpTraits<OP_F16> {
   static constexpr int ES = 2, MMA = ptx::MMA_F16;
-  static constexpr uint32_t AB_FMT = 0, D_FMT = 1;
+  static constexpr uint32_t AB_FMT = 0, D_FMT = 1, B_MN_MAJOR = 1;
   using Out = __half;
 };
 template <>
 struct OpTraits<OP_BF16> {
   static constexpr int ES = 2, MMA = ptx::MMA_F16;
-  static constexpr uint32_t AB_FMT = 1, D_FMT = 1;
+  static constexpr uint32_t AB_FMT = 1, D_FMT = 1, B_MN_MAJOR = 1;
   using Out = __nv_bfloat16;
 };
 template <>
 struct OpTraits<OP_TF32> {
+  // The TF32 kind returned zeros when B was described MN-major with the plain
+  // 128-byte swizzle (measured with a one-CTA probe on B200), while K-major B is
+  // exact.  fp32 operands pass through a split pre-pass anyway, so that pass writes
+  // B transposed ([N,K]) and the kernel reads it K-major.
   static constexpr int ES = 4, MMA = ptx::MMA_TF32;
-  static constexpr uint32_t AB_FMT = 2, D_FMT = 1;
+  static constexpr uint32_t AB_FMT = 2, D_FMT = 1, B_MN_MAJOR = 0;
   using Out = float;
 };
 template <>
 struct OpTraits<OP_I8> {
   static constexpr int ES = 1, MMA = ptx::MMA_I8;
-  static constexpr uint32_t AB_FMT = 1, D_FMT = 2;
+  static constexpr uint32_t AB_FMT = 1, D_FMT = 2, B_MN_MAJOR = 1;
   using Out = int8_t;
 };
 
@@ -75,13 +81,26 @@ struct UmmaGemmParams {
   int32_t M, N, K, batch;
   int32_t m_tiles, n_tiles, k_blocks;
   int32_t passes;        // 1, or 3 when fp32 runs as (A_lo,B_hi), (A_hi,B_lo), (A_hi,B_hi)
+  int32_t k_chunk_blocks;// stages of K summed inside TMEM before the sum moves to registers
   uint32_t total_tiles;  // batch * m_tiles * n_tiles
   void* C;
   uint32_t* status;
   uint64_t wait_limit_ns;
 };
 
-template <int BLOCK_N, int STAGES>
+// fp32 (three TF32 passes) keeps its running sum in registers: the tensor core adds
+// into its fp32 accumulator with truncation, a bias that grows with the number of
+// accumulating MMAs (measured: 1.4e-5 relative at K = 2048).  So K is cut into chunks
+// of `k_chunk_blocks` stages; each chunk is accumulated in TMEM from zero, and eight
+// epilogue warps add the chunks with round-to-nearest FADDs while the next chunk runs
+// in the other TMEM buffer.
+template <int OP>
+struct UmmaEpilogue {
+  static constexpr bool CHUNKED = (OP == OP_TF32);
+  static constexpr int WARPS = CHUNKED ? 8 : 4;
+};
+
+template <int OP, int BLOCK_N, int STAGES>
 struct UmmaGemmConfig {
   static constexpr int BLOCK_M = 128;
   static constexpr int A_BYTES = BLOCK_M * 128;
@@ -90,7 +109,8 @@ struct UmmaGemmConfig {
   static constexpr int NUM_BARRIERS = 2 * STAGES + 4;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + NUM_BARRIERS * 8 + 16 + 1024;
   static constexpr int TMEM_COLS = 2 * BLOCK_N;
-  static constexpr int THREADS = 192;
+  static constexpr int EPI_WARPS = UmmaEpilogue<OP>::WARPS;
+  static constexpr int THREADS = 64 + 32 * EPI_WARPS;
 };
 
 __device__ __forceinline__ void decode_tile(uint32_t tile, const UmmaGemmParams& p, int& b, int& mt,
@@ -165,13 +185,14 @@ __device__ __forceinline__ void store_row_chunk(typename OpTraits<OP>::Out* dst,
 }
 
 template <int OP, int BLOCK_N, int STAGES>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(64 + 32 * UmmaEpilogue<OP>::WARPS, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
                  const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
                  const UmmaGemmParams p) {
   using T = OpTraits<OP>;
-  using Cfg = UmmaGemmConfig<BLOCK_N, STAGES>;
+  using Cfg = UmmaGemmConfig<OP, BLOCK_N, STAGES>;
   using Out = typename T::Out;
+  constexpr bool CHUNKED = UmmaEpilogue<OP>::CHUNKED;
   constexpr int ES = T::ES;
   constexpr int BLOCK_M = Cfg::BLOCK_M;
   constexpr int BK = 128 / ES;                  // K elements per stage
@@ -180,7 +201,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
   constexpr int CHUNK_BYTES = BK * 128;         // bytes of one B box = LBO of the B descriptor
   constexpr int KSTEPS = 4;                     // 128 B of K per stage / 32 B per MMA
   constexpr int B_KSTEP_BYTES = (32 / ES) * 128;// K rows of one MMA x 128 B
-  constexpr uint32_t IDESC = ptx::make_instr_desc(T::D_FMT, T::AB_FMT, 0u, 1u, BLOCK_M, BLOCK_N);
+  constexpr bool B_MN = T::B_MN_MAJOR != 0;
+  constexpr uint32_t IDESC =
+      ptx::make_instr_desc(T::D_FMT, T::AB_FMT, 0u, T::B_MN_MAJOR, BLOCK_M, BLOCK_N);
   static_assert(BLOCK_N % 16 == 0 && BLOCK_N >= 32 && BLOCK_N <= 256, "UMMA N range");
   static_assert((Cfg::TMEM_COLS & (Cfg::TMEM_COLS - 1)) == 0 && Cfg::TMEM_COLS >= 32, "TMEM cols");
   static_assert(BLOCK_N % CHUNK_N == 0, "B tile must be whole 128-byte boxes");
@@ -209,7 +232,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
     }
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(tfull_bar(b), 1);
-      ptx::mbar_init(tempty_bar(b), 128);
+      ptx::mbar_init(tempty_bar(b), 32 * Cfg::EPI_WARPS);
     }
     ptx::fence_mbar_init();
   }
@@ -230,7 +253,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
   ptx::tc_fence_after();
   const uint32_t tmem_base = *slot_ptr;
 
-  const int k_iters = p.k_blocks * p.passes;
+  // work items of a CTA: (tile, K chunk); one chunk per tile unless CHUNKED
+  const int kc = CHUNKED ? p.k_chunk_blocks : p.k_blocks;
+  const int chunks = (p.k_blocks + kc - 1) / kc;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
@@ -253,10 +278,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
             const CUtensorMap* mb = (p.passes > 1 && pass == 1) ? &tmB1 : &tmB0;
             ptx::mbar_expect_tx(full_bar(stage), Cfg::STAGE_BYTES);
             ptx::tma_load_3d(a_smem(stage), ma, full_bar(stage), kb * BK, mt * BLOCK_M, b);
+            if constexpr (B_MN) {
 #pragma unroll
-            for (int c = 0; c < NCHUNK; ++c)
-              ptx::tma_load_3d(b_smem(stage) + c * CHUNK_BYTES, mb, full_bar(stage),
-                               nt * BLOCK_N + c * CHUNK_N, kb * BK, b);
+              for (int c = 0; c < NCHUNK; ++c)
+                ptx::tma_load_3d(b_smem(stage) + c * CHUNK_BYTES, mb, full_bar(stage),
+                                 nt * BLOCK_N + c * CHUNK_N, kb * BK, b);
+            } else {
+              // B^T[N,K]: one box of BLOCK_N rows x 128 B of K, the same shape as the A tile
+              ptx::tma_load_3d(b_smem(stage), mb, full_bar(stage), kb * BK, nt * BLOCK_N, b);
+            }
             if (++stage == STAGES) {
               stage = 0;
               phase ^= 1u;
@@ -272,38 +302,43 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
       uint32_t phase = 0;
       uint32_t local = 0;
       bool ok = true;
-      for (uint32_t tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x, ++local) {
-        const uint32_t buf = local & 1u;
-        const uint32_t acc_phase = (local >> 1) & 1u;
-        if (!ptx::mbar_wait(tempty_bar(buf), acc_phase ^ 1u, p.wait_limit_ns)) {
-          atomicOr(p.status, ST_MMA_TIMEOUT);
-          ok = false;
-          break;
-        }
-        ptx::tc_fence_after();
-        const uint32_t d_tmem = tmem_base + buf * BLOCK_N;
-        for (int it = 0; it < k_iters; ++it) {
-          if (!ptx::mbar_wait(full_bar(stage), phase, p.wait_limit_ns)) {
+      for (uint32_t tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
+        for (int ch = 0; ok && ch < chunks; ++ch, ++local) {
+          const uint32_t buf = local & 1u;
+          const uint32_t acc_phase = (local >> 1) & 1u;
+          if (!ptx::mbar_wait(tempty_bar(buf), acc_phase ^ 1u, p.wait_limit_ns)) {
             atomicOr(p.status, ST_MMA_TIMEOUT);
             ok = false;
             break;
           }
           ptx::tc_fence_after();
-          const uint32_t a0 = a_smem(stage);
-          const uint32_t b0 = b_smem(stage);
+          const uint32_t d_tmem = tmem_base + buf * BLOCK_N;
+          const int kb_end = min(p.k_blocks, (ch + 1) * kc);
+          const int k_iters = (kb_end - ch * kc) * p.passes;
+          for (int it = 0; it < k_iters; ++it) {
+            if (!ptx::mbar_wait(full_bar(stage), phase, p.wait_limit_ns)) {
+              atomicOr(p.status, ST_MMA_TIMEOUT);
+              ok = false;
+              break;
+            }
+            ptx::tc_fence_after();
+            const uint32_t a0 = a_smem(stage);
+            const uint32_t b0 = b_smem(stage);
 #pragma unroll
-          for (int k = 0; k < KSTEPS; ++k) {
-            const uint64_t adesc = ptx::make_smem_desc(a0 + k * 32, 16, 1024);
-            const uint64_t bdesc = ptx::make_smem_desc(b0 + k * B_KSTEP_BYTES, CHUNK_BYTES, 1024);
-            ptx::tc_mma<T::MMA>(d_tmem, adesc, bdesc, IDESC, (it > 0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < KSTEPS; ++k) {
+              const uint64_t adesc = ptx::make_smem_desc(a0 + k * 32, 16, 1024);
+              const uint64_t bdesc = B_MN ? ptx::make_smem_desc(b0 + k * B_KSTEP_BYTES, CHUNK_BYTES, 1024)
+                                          : ptx::make_smem_desc(b0 + k * 32, 16, 1024);
+              ptx::tc_mma<T::MMA>(d_tmem, adesc, bdesc, IDESC, (it > 0 || k > 0) ? 1u : 0u);
+            }
+            ptx::tc_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1u;
+            }
           }
-          ptx::tc_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
-          if (++stage == STAGES) {
-            stage = 0;
-            phase ^= 1u;
-          }
+          if (ok) ptx::tc_commit(tfull_bar(buf));  // this chunk's sum is complete
         }
-        if (ok) ptx::tc_commit(tfull_bar(buf));  // accumulator complete
       }
     }
   } else {
@@ -312,33 +347,82 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
     uint32_t local = 0;
     bool ok = true;
     Out* const Cbase = reinterpret_cast<Out*>(p.C);
-    for (uint32_t tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x, ++local) {
-      int b, mt, nt;
-      decode_tile(tile, p, b, mt, nt);
-      const uint32_t buf = local & 1u;
-      const uint32_t acc_phase = (local >> 1) & 1u;
-      // the verdict is made warp-uniform: tcgen05.ld below needs all 32 lanes
-      const bool landed = ptx::mbar_wait(tfull_bar(buf), acc_phase, p.wait_limit_ns);
-      if (!__all_sync(0xffffffffu, landed)) {
-        if (lane == 0) atomicOr(p.status, ST_EPILOGUE_TIMEOUT);
-        ok = false;
-        break;
-      }
-      ptx::tc_fence_after();
-      const int row = mt * BLOCK_M + quad * 32 + lane;
-      const int col0 = nt * BLOCK_N;
-      const uint32_t taddr = tmem_base + buf * BLOCK_N + (static_cast<uint32_t>(quad * 32) << 16);
-      Out* crow = Cbase + (static_cast<size_t>(b) * p.M + static_cast<size_t>(row)) * p.N + col0;
+    if constexpr (!CHUNKED) {
+      for (uint32_t tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x, ++local) {
+        int b, mt, nt;
+        decode_tile(tile, p, b, mt, nt);
+        const uint32_t buf = local & 1u;
+        const uint32_t acc_phase = (local >> 1) & 1u;
+        // the verdict is made warp-uniform: tcgen05.ld below needs all 32 lanes
+        const bool landed = ptx::mbar_wait(tfull_bar(buf), acc_phase, p.wait_limit_ns);
+        if (!__all_sync(0xffffffffu, landed)) {
+          if (lane == 0) atomicOr(p.status, ST_EPILOGUE_TIMEOUT);
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after();
+        const int row = mt * BLOCK_M + quad * 32 + lane;
+        const int col0 = nt * BLOCK_N;
+        const uint32_t taddr = tmem_base + buf * BLOCK_N + (static_cast<uint32_t>(quad * 32) << 16);
+        Out* crow = Cbase + (static_cast<size_t>(b) * p.M + static_cast<size_t>(row)) * p.N + col0;
 #pragma unroll 1
-      for (int c = 0; c < BLOCK_N / 32; ++c) {
-        uint32_t v[32];
-        ptx::tmem_ld_32x32(taddr + c * 32, v);
-        ptx::tmem_ld_wait();
-        const int cols_left = p.N - (col0 + c * 32);
-        if (row < p.M && cols_left > 0) store_row_chunk<OP>(crow + c * 32, v, cols_left);
+        for (int c = 0; c < BLOCK_N / 32; ++c) {
+          uint32_t v[32];
+          ptx::tmem_ld_32x32(taddr + c * 32, v);
+          ptx::tmem_ld_wait();
+          const int cols_left = p.N - (col0 + c * 32);
+          if (row < p.M && cols_left > 0) store_row_chunk<OP>(crow + c * 32, v, cols_left);
+        }
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(tempty_bar(buf));
       }
-      ptx::tc_fence_before();
-      ptx::mbar_arrive(tempty_bar(buf));
+    } else {
+      // Eight warps: warps 2-5 own columns [0, BLOCK_N/2), warps 6-9 the rest; each
+      // thread keeps its row's half of the tile in registers across the K chunks.
+      constexpr int HALF_N = BLOCK_N / 2;
+      const int half = (warp - 2) >> 2;
+      float acc[HALF_N];
+      for (uint32_t tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
+        int b, mt, nt;
+        decode_tile(tile, p, b, mt, nt);
+#pragma unroll
+        for (int j = 0; j < HALF_N; ++j) acc[j] = 0.f;
+        for (int ch = 0; ch < chunks; ++ch, ++local) {
+          const uint32_t buf = local & 1u;
+          const uint32_t acc_phase = (local >> 1) & 1u;
+          const bool landed = ptx::mbar_wait(tfull_bar(buf), acc_phase, p.wait_limit_ns);
+          if (!__all_sync(0xffffffffu, landed)) {
+            if (lane == 0) atomicOr(p.status, ST_EPILOGUE_TIMEOUT);
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t taddr = tmem_base + buf * BLOCK_N + half * HALF_N +
+                                 (static_cast<uint32_t>(quad * 32) << 16);
+#pragma unroll
+          for (int c = 0; c < HALF_N / 32; ++c) {
+            uint32_t v[32];
+            ptx::tmem_ld_32x32(taddr + c * 32, v);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) acc[c * 32 + j] += __uint_as_float(v[j]);
+          }
+          ptx::tc_fence_before();
+          ptx::mbar_arrive(tempty_bar(buf));
+        }
+        if (!ok) break;
+        const int row = mt * BLOCK_M + quad * 32 + lane;
+        const int col0 = nt * BLOCK_N + half * HALF_N;
+        if (row < p.M) {
+          float4* crow = reinterpret_cast<float4*>(
+              reinterpret_cast<float*>(Cbase) +
+              (static_cast<size_t>(b) * p.M + static_cast<size_t>(row)) * p.N + col0);
+#pragma unroll
+          for (int g = 0; g < HALF_N / 4; ++g)
+            if (col0 + g * 4 < p.N)
+              crow[g] = make_float4(acc[4 * g], acc[4 * g + 1], acc[4 * g + 2], acc[4 * g + 3]);
+        }
+      }
     }
   }
 

@@ -92,7 +92,9 @@ def matmul(a, b, *, algo: int = ALGO_AUTO, out=None):
     else:
         if tuple(out.shape) != shape_c or out.dtype != from_tvb[dtc] or not out.is_contiguous():
             raise RuntimeError("out has the wrong shape, dtype or layout")
-    stream = torch.cuda.current_stream(a.device).cuda_stream
+    # torch reports its legacy default stream as handle 0, which the C ABI reads as
+    # "the library's own stream"; CUDA's explicit handle for the legacy stream is 1
+    stream = torch.cuda.current_stream(a.device).cuda_stream or 1
     check(lib.tvb_matmul_algo(dev, a.data_ptr(), b.data_ptr(), out.data_ptr(), dta, dtb, dtc,
                               batch, M, K, N, C.c_void_p(stream), algo))
     return out
