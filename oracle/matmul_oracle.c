@@ -1,0 +1,353 @@
+/*
+ * TEST INFRASTRUCTURE — not part of the product.  Only tests/, the smoke check and the
+ * benchmark's CPU-baseline leg may call this file; the product never does.
+ *
+ * A plain-C restatement of the reference's matmul for checking the CUDA path:
+ *
+ *   tvo_matmul_cpu    the CPU/OpenMP backend, MulImpl<Device::CPU>::execute
+ *                     (src/backend/cpu/mul.cpp:97-145): half inputs are cast to fp32
+ *                     first and the result is then FLOAT32 (mul.cpp:110-113); outputs
+ *                     below 1 Mi elements take mul_kernel_basic (mul.cpp:7-25), larger
+ *                     ones mul_kernel_tiled<64> (mul.cpp:27-85) with its 64-long partial
+ *                     sums cast to the result type and added there (mul.cpp:74-78) and
+ *                     its accumulator of A's type only (mul.cpp:64).
+ *   tvo_matmul_cuda   the semantics of the CUDA kernel mul_cuda_3d
+ *                     (src/backend/cuda/mul.cu:8-48): one accumulator per output of type
+ *                     decltype(compute_type_t<T>() + compute_type_t<R>()) (mul.cu:19), k in
+ *                     increasing order, static_cast to compute_type(dtype a, dtype b)
+ *                     (mul.cu:46,63) — half x half gives half, rounded to nearest even.
+ *
+ * Parity pin: tests/golden holds outputs of the reference library itself (built from its
+ * own sources by oracle/Makefile, run by tests/golden/make_golden.py); tests/test_oracle.py
+ * checks this file against them.
+ */
+#include <math.h>
+#include <omp.h>
+#include <stddef.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+enum { DT_I8 = 0, DT_I16, DT_I32, DT_I64, DT_BF16, DT_F16, DT_F32, DT_F64 };
+
+/* ---- via::compute_type, include/core/type_traits.h:270-287 (the code, not the comment
+ * block above it, which disagrees with the code) ---------------------------------------*/
+int tvo_compute_type(int a, int b) {
+  if (a < 0 || a > 7 || b < 0 || b > 7) return -1;
+  if (a == b) return a;
+  int mx = a > b ? a : b;
+  if (a <= DT_I64 && b <= DT_I64) return mx;
+  if (a > DT_I64 && b > DT_I64) return mx > DT_F32 ? mx : DT_F32;
+  if (a == DT_I64 || b == DT_I64) return DT_F64;
+  return mx > DT_F32 ? mx : DT_F32;
+}
+
+/* via::calc_dtype_size, include/core/type_traits.h:158-171 */
+int tvo_dtype_size(int d) {
+  static const int s[8] = {1, 2, 4, 8, 2, 2, 4, 8};
+  return (d < 0 || d > 7) ? 0 : s[d];
+}
+
+/* ---- half <-> float, bit exact ----------------------------------------------------------*/
+static float bits_to_f32(uint32_t u) { float f; memcpy(&f, &u, 4); return f; }
+static uint32_t f32_to_bits(float f) { uint32_t u; memcpy(&u, &f, 4); return u; }
+
+float tvo_bf16_to_f32(uint16_t h) { return bits_to_f32((uint32_t)h << 16); }
+
+float tvo_f16_to_f32(uint16_t h) {
+  uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+  uint32_t exp = (h >> 10) & 0x1Fu;
+  uint32_t man = h & 0x3FFu;
+  if (exp == 0) {
+    if (man == 0) return bits_to_f32(sign);
+    /* subnormal: value = man * 2^-24 */
+    float v = (float)man * (1.0f / 16777216.0f);
+    return sign ? -v : v;
+  }
+  if (exp == 31) return bits_to_f32(sign | 0x7F800000u | (man << 13));
+  return bits_to_f32(sign | ((exp + 112u) << 23) | (man << 13));
+}
+
+/* round to nearest even, as static_cast<__nv_bfloat16>(float) does on the device */
+uint16_t tvo_f32_to_bf16(float f) {
+  uint32_t u = f32_to_bits(f);
+  if ((u & 0x7FFFFFFFu) > 0x7F800000u) return (uint16_t)((u >> 16) | 0x0040u); /* NaN */
+  uint32_t lsb = (u >> 16) & 1u;
+  u += 0x7FFFu + lsb;
+  return (uint16_t)(u >> 16);
+}
+
+/* round to nearest even, as static_cast<__half>(float) does on the device */
+uint16_t tvo_f32_to_f16(float f) {
+  uint32_t u = f32_to_bits(f);
+  uint32_t sign = (u >> 16) & 0x8000u;
+  uint32_t a = u & 0x7FFFFFFFu;
+  if (a > 0x7F800000u) return (uint16_t)(sign | 0x7E00u);           /* NaN */
+  if (a >= 0x477FF000u) return (uint16_t)(sign | 0x7C00u);          /* >= 65520 -> inf */
+  if (a < 0x33000001u) return (uint16_t)sign;                        /* <= 2^-25 -> 0   */
+  int32_t e = (int32_t)(a >> 23) - 127;
+  uint32_t m = (a & 0x7FFFFFu) | 0x800000u; /* 24-bit significand */
+  uint32_t shift, half_exp;
+  if (e < -14) { shift = (uint32_t)(13 + (-14 - e)); half_exp = 0; }  /* subnormal half */
+  else { shift = 13; half_exp = (uint32_t)(e + 15); }
+  uint32_t q = m >> shift;
+  uint32_t rem = m & ((1u << shift) - 1u);
+  uint32_t halfway = 1u << (shift - 1);
+  if (rem > halfway || (rem == halfway && (q & 1u))) q++;
+  uint32_t r;
+  if (half_exp == 0) r = q;                       /* q may carry into exponent 1: still right */
+  else r = ((half_exp - 1u) << 10) + q;           /* q has the implicit bit: adds 1 to the exponent */
+  return (uint16_t)(sign | r);
+}
+
+void tvo_bf16_to_f32_n(const uint16_t* s, float* d, size_t n) { for (size_t i = 0; i < n; ++i) d[i] = tvo_bf16_to_f32(s[i]); }
+void tvo_f16_to_f32_n(const uint16_t* s, float* d, size_t n) { for (size_t i = 0; i < n; ++i) d[i] = tvo_f16_to_f32(s[i]); }
+void tvo_f32_to_bf16_n(const float* s, uint16_t* d, size_t n) { for (size_t i = 0; i < n; ++i) d[i] = tvo_f32_to_bf16(s[i]); }
+void tvo_f32_to_f16_n(const float* s, uint16_t* d, size_t n) { for (size_t i = 0; i < n; ++i) d[i] = tvo_f32_to_f16(s[i]); }
+
+/* ---- the two reference kernels, one instance per (A type, B type) ------------------------
+ * After the CPU backend's half -> fp32 cast only six element types reach the kernels. */
+typedef int8_t i8;
+typedef int16_t i16;
+typedef int32_t i32;
+typedef int64_t i64;
+typedef float f32;
+typedef double f64;
+
+/* (A type, B type, result type = via::compute_type of the pair) */
+#define TVO_PAIRS(X) \
+  X(i8, i8, i8) X(i8, i16, i16) X(i8, i32, i32) X(i8, i64, i64) X(i8, f32, f32) X(i8, f64, f64) \
+  X(i16, i8, i16) X(i16, i16, i16) X(i16, i32, i32) X(i16, i64, i64) X(i16, f32, f32) X(i16, f64, f64) \
+  X(i32, i8, i32) X(i32, i16, i32) X(i32, i32, i32) X(i32, i64, i64) X(i32, f32, f32) X(i32, f64, f64) \
+  X(i64, i8, i64) X(i64, i16, i64) X(i64, i32, i64) X(i64, i64, i64) X(i64, f32, f64) X(i64, f64, f64) \
+  X(f32, i8, f32) X(f32, i16, f32) X(f32, i32, f32) X(f32, i64, f64) X(f32, f32, f32) X(f32, f64, f64) \
+  X(f64, i8, f64) X(f64, i16, f64) X(f64, i32, f64) X(f64, i64, f64) X(f64, f32, f64) X(f64, f64, f64)
+
+/* mul_kernel_basic, src/backend/cpu/mul.cpp:7-25 — and, with `promote_both`, also the
+ * arithmetic of mul_cuda_3d (src/backend/cuda/mul.cu:19-46): accumulator of the type the
+ * usual arithmetic conversions give for (A element + B element), k ascending, one cast at
+ * the end. */
+#define TVO_BASIC(TA, TB, TS)                                                                   \
+  static void basic_##TA##_##TB(const void* av, const void* bv, void* cv, size_t batch,         \
+                                size_t rows, size_t common, size_t cols) {                      \
+    const TA* a = (const TA*)av;                                                                \
+    const TB* b = (const TB*)bv;                                                                \
+    TS* c = (TS*)cv;                                                                            \
+    _Pragma("omp parallel for collapse(2)")                                                     \
+    for (size_t bb = 0; bb < batch; ++bb)                                                       \
+      for (size_t i = 0; i < rows; ++i)                                                         \
+        for (size_t j = 0; j < cols; ++j) {                                                     \
+          typedef __typeof__((TA)0 + (TB)0) P;                                                  \
+          P sum = 0;                                                                            \
+          for (size_t k = 0; k < common; ++k)                                                   \
+            sum += (P)a[bb * rows * common + i * common + k] *                                  \
+                   (P)b[bb * common * cols + k * cols + j];                                     \
+          c[bb * rows * cols + i * cols + j] = (TS)sum;                                         \
+        }                                                                                       \
+  }
+
+/* mul_kernel_tiled<T,R,S,64>, src/backend/cpu/mul.cpp:27-85: 64x64 output tiles, K in
+ * steps of 64 through copied tiles; the partial sum has the type of A's elements ALONE
+ * (mul.cpp:64) and is cast to the result type, then stored (first step) or added in the
+ * result type (later steps, mul.cpp:74-78). */
+#define TVO_TILED(TA, TB, TS)                                                                   \
+  static void tiled_##TA##_##TB(const void* av, const void* bv, void* cv, size_t batch,         \
+                                size_t rows, size_t common, size_t cols) {                      \
+    enum { TILE = 64 };                                                                         \
+    const TA* a = (const TA*)av;                                                                \
+    const TB* b = (const TB*)bv;                                                                \
+    TS* c = (TS*)cv;                                                                            \
+    _Pragma("omp parallel for collapse(3)")                                                     \
+    for (size_t bb = 0; bb < batch; ++bb)                                                       \
+      for (size_t by = 0; by < rows; by += TILE)                                                \
+        for (size_t bx = 0; bx < cols; bx += TILE) {                                            \
+          const size_t row_end = by + TILE < rows ? by + TILE : rows;                           \
+          const size_t col_end = bx + TILE < cols ? bx + TILE : cols;                           \
+          TA* at = (TA*)malloc(sizeof(TA) * TILE * TILE);                                       \
+          TB* bt = (TB*)malloc(sizeof(TB) * TILE * TILE);                                       \
+          for (size_t k0 = 0; k0 < common; k0 += TILE) {                                        \
+            const size_t k_end = k0 + TILE < common ? k0 + TILE : common;                       \
+            for (size_t i = by; i < row_end; ++i)                                               \
+              for (size_t k = k0; k < k_end; ++k)                                               \
+                at[(i - by) * TILE + (k - k0)] = a[bb * rows * common + i * common + k];        \
+            for (size_t k = k0; k < k_end; ++k)                                                 \
+              for (size_t j = bx; j < col_end; ++j)                                             \
+                bt[(k - k0) * TILE + (j - bx)] = b[bb * common * cols + k * cols + j];          \
+            for (size_t i = by; i < row_end; ++i)                                               \
+              for (size_t j = bx; j < col_end; ++j) {                                           \
+                TA sum = 0;                                                                     \
+                for (size_t k = 0; k < k_end - k0; ++k)                                         \
+                  sum += (TA)at[(i - by) * TILE + k] * (TA)bt[k * TILE + (j - bx)];             \
+                const size_t idx = bb * rows * cols + i * cols + j;                             \
+                if (k0 == 0) c[idx] = (TS)sum;                                                  \
+                else c[idx] += (TS)sum;                                                         \
+              }                                                                                 \
+          }                                                                                     \
+          free(at);                                                                             \
+          free(bt);                                                                             \
+        }                                                                                       \
+  }
+
+TVO_PAIRS(TVO_BASIC)
+TVO_PAIRS(TVO_TILED)
+
+typedef void (*kern_fn)(const void*, const void*, void*, size_t, size_t, size_t, size_t);
+#define TVO_BASIC_PTR(TA, TB, TS) basic_##TA##_##TB,
+#define TVO_TILED_PTR(TA, TB, TS) tiled_##TA##_##TB,
+static const kern_fn basic_tab[36] = {TVO_PAIRS(TVO_BASIC_PTR)};
+static const kern_fn tiled_tab[36] = {TVO_PAIRS(TVO_TILED_PTR)};
+
+/* dtype -> index among the six kernel element types (halves have been cast to fp32) */
+static int kidx(int dt) {
+  switch (dt) {
+    case DT_I8: return 0;
+    case DT_I16: return 1;
+    case DT_I32: return 2;
+    case DT_I64: return 3;
+    case DT_F32: return 4;
+    case DT_F64: return 5;
+    default: return -1;
+  }
+}
+
+static int is_half(int dt) { return dt == DT_BF16 || dt == DT_F16; }
+
+/* ops::Typecast(half -> FLOAT32) of src/backend/cpu/typecast.cpp:79-98, as used by
+ * mul.cpp:110-111.  Returns a malloc'd fp32 copy. */
+static float* widen_half(const void* src, int dt, size_t n) {
+  float* d = (float*)malloc(sizeof(float) * (n ? n : 1));
+  if (!d) return NULL;
+  if (dt == DT_BF16) tvo_bf16_to_f32_n((const uint16_t*)src, d, n);
+  else tvo_f16_to_f32_n((const uint16_t*)src, d, n);
+  return d;
+}
+
+/* threads the reference would use: min(omp_get_max_threads(), 16), mul.cpp:114 */
+int tvo_threads(void) {
+  int m = omp_get_max_threads();
+  return m < 16 ? m : 16;
+}
+
+/* ops::Mul shape rules, src/ops.cpp:540-556.  rank 2: dims = {M,K} / {K,N}; rank 3 adds a
+ * leading batch.  Returns 0 if valid, else the number of the rule that fails:
+ * 1 rank mismatch (:544), 2 rank not 2 or 3 (:546), 3 batch mismatch (:549),
+ * 4 common dim mismatch (:551, :554), 5 a dimension <= 0 (calc_numel, type_traits.h:293-300). */
+int tvo_check_shapes(int rank_a, const int64_t* da, int rank_b, const int64_t* db) {
+  for (int i = 0; i < rank_a; ++i) if (da[i] <= 0) return 5;
+  for (int i = 0; i < rank_b; ++i) if (db[i] <= 0) return 5;
+  if (rank_a != rank_b) return 1;
+  if (rank_a != 2 && rank_a != 3) return 2;
+  if (rank_a == 3) {
+    if (da[0] != db[0]) return 3;
+    if (da[2] != db[1]) return 4;
+  } else if (da[1] != db[0]) return 4;
+  return 0;
+}
+
+static int run_kernels(const void* a, int dta, const void* b, int dtb, void* c, size_t batch,
+                       size_t M, size_t K, size_t N, int force_basic) {
+  const int ia = kidx(dta), ib = kidx(dtb);
+  if (ia < 0 || ib < 0) return 1;
+  omp_set_num_threads(tvo_threads());                         /* mul.cpp:114 */
+  const size_t total = batch * M * N;
+  if (force_basic || total < (size_t)1024 * 1024) basic_tab[ia * 6 + ib](a, b, c, batch, M, K, N); /* mul.cpp:88-96 */
+  else tiled_tab[ia * 6 + ib](a, b, c, batch, M, K, N);
+  return 0;
+}
+
+/* MulImpl<Device::CPU>::execute, src/backend/cpu/mul.cpp:97-145.  *dtc receives the result
+ * dtype (FLOAT32 when an input was half); c must hold batch*M*N elements of it. */
+int tvo_matmul_cpu(const void* a, int dta, const void* b, int dtb, void* c, int* dtc, int64_t batch,
+                   int64_t M, int64_t K, int64_t N) {
+  if (batch <= 0 || M <= 0 || K <= 0 || N <= 0) return 2;
+  float *wa = NULL, *wb = NULL;
+  int ea = dta, eb = dtb;
+  if (is_half(dta)) { wa = widen_half(a, dta, (size_t)(batch * M * K)); a = wa; ea = DT_F32; }
+  if (is_half(dtb)) { wb = widen_half(b, dtb, (size_t)(batch * K * N)); b = wb; eb = DT_F32; }
+  if (dtc) *dtc = tvo_compute_type(ea, eb);                   /* mul.cpp:112 */
+  int rc = run_kernels(a, ea, b, eb, c, (size_t)batch, (size_t)M, (size_t)K, (size_t)N, 0);
+  free(wa);
+  free(wb);
+  return rc;
+}
+
+/* mul_cuda_3d + MulImpl<Device::CUDA>::execute semantics, src/backend/cuda/mul.cu:8-124,
+ * computed on the CPU: result dtype compute_type(dta, dtb) (mul.cu:63), accumulator
+ * promoted from both operands (mul.cu:19), one sequential sum over k, a single final cast.
+ * FLOAT64 results use the true column count (the reference passes rows for cols at
+ * mul.cu:91, a defect that is not reproduced). */
+int tvo_matmul_cuda(const void* a, int dta, const void* b, int dtb, void* c, int* dtc, int64_t batch,
+                    int64_t M, int64_t K, int64_t N) {
+  if (batch <= 0 || M <= 0 || K <= 0 || N <= 0) return 2;
+  const int out_dt = tvo_compute_type(dta, dtb);
+  if (out_dt < 0) return 1;
+  if (dtc) *dtc = out_dt;
+  float *wa = NULL, *wb = NULL;
+  int ea = dta, eb = dtb;
+  if (is_half(dta)) { wa = widen_half(a, dta, (size_t)(batch * M * K)); a = wa; ea = DT_F32; }
+  if (is_half(dtb)) { wb = widen_half(b, dtb, (size_t)(batch * K * N)); b = wb; eb = DT_F32; }
+  const size_t n = (size_t)(batch * M * N);
+  int rc;
+  if (is_half(out_dt)) {
+    /* same-type halves: fp32 accumulate, then round to the half type */
+    float* tmp = (float*)malloc(sizeof(float) * n);
+    rc = run_kernels(a, ea, b, eb, tmp, (size_t)batch, (size_t)M, (size_t)K, (size_t)N, 1);
+    if (rc == 0) {
+      if (out_dt == DT_BF16) tvo_f32_to_bf16_n(tmp, (uint16_t*)c, n);
+      else tvo_f32_to_f16_n(tmp, (uint16_t*)c, n);
+    }
+    free(tmp);
+  } else {
+    /* after widening, compute_type(ea, eb) == out_dt for every pair, so the basic kernel's
+     * result type is already the CUDA result type */
+    rc = (tvo_compute_type(ea, eb) == out_dt)
+             ? run_kernels(a, ea, b, eb, c, (size_t)batch, (size_t)M, (size_t)K, (size_t)N, 1)
+             : 3;
+  }
+  free(wa);
+  free(wb);
+  return rc;
+}
+
+/* ---- seeded synthetic inputs ---------------------------------------------------------------
+ * Element i = f(SplitMix64 output number first+i for `seed`); the same function as the
+ * device generator, so host and device inputs are bit-identical.
+ * dist 0: floats uniform in [-1,1) on a 2^-23 grid (rounded to nearest even for bf16/f16);
+ * dist 1 (and every integer dtype): integers uniform in [-10,10]. */
+static uint64_t splitmix64_at(uint64_t seed, uint64_t index) {
+  uint64_t z = seed + (index + 1ull) * 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+
+int tvo_fill_splitmix(void* dst, int dtype, uint64_t count, uint64_t seed, uint64_t first, int dist) {
+  if (dtype < 0 || dtype > 7) return 1;
+  const int is_float = dtype >= DT_BF16;
+#pragma omp parallel for
+  for (uint64_t i = 0; i < count; ++i) {
+    const uint64_t u = splitmix64_at(seed, first + i);
+    if (is_float && dist == 0) {
+      const float f = (float)(uint32_t)(u >> 40) * (1.0f / 8388608.0f) - 1.0f;
+      switch (dtype) {
+        case DT_BF16: ((uint16_t*)dst)[i] = tvo_f32_to_bf16(f); break;
+        case DT_F16: ((uint16_t*)dst)[i] = tvo_f32_to_f16(f); break;
+        case DT_F32: ((float*)dst)[i] = f; break;
+        default: ((double*)dst)[i] = (double)f; break;
+      }
+    } else {
+      const int v = (int)(u % 21ull) - 10;
+      switch (dtype) {
+        case DT_I8: ((int8_t*)dst)[i] = (int8_t)v; break;
+        case DT_I16: ((int16_t*)dst)[i] = (int16_t)v; break;
+        case DT_I32: ((int32_t*)dst)[i] = v; break;
+        case DT_I64: ((int64_t*)dst)[i] = v; break;
+        case DT_BF16: ((uint16_t*)dst)[i] = tvo_f32_to_bf16((float)v); break;
+        case DT_F16: ((uint16_t*)dst)[i] = tvo_f32_to_f16((float)v); break;
+        case DT_F32: ((float*)dst)[i] = (float)v; break;
+        default: ((double*)dst)[i] = (double)v; break;
+      }
+    }
+  }
+  return 0;
+}

@@ -49,6 +49,9 @@ def _torch_maps():
 
 def check_shapes(shape_a, shape_b) -> tuple[int, int, int, int]:
     """The validity rules of ops::Mul (src/ops.cpp:544-556). Returns (batch, M, K, N)."""
+    for d in tuple(shape_a) + tuple(shape_b):
+        if d <= 0:  # via::calc_numel, include/core/type_traits.h:293-300
+            raise RuntimeError("Invalid tensor dimension")
     if len(shape_a) != len(shape_b):
         raise RuntimeError(
             f"Tensors a and b must have the same rank,but got {len(shape_a)} and {len(shape_b)}")
@@ -61,7 +64,8 @@ def check_shapes(shape_a, shape_b) -> tuple[int, int, int, int]:
             raise RuntimeError(f"Tensors common dim must match,but {shape_a[2]} and {shape_b[1]}")
         return int(shape_a[0]), int(shape_a[1]), int(shape_a[2]), int(shape_b[2])
     if shape_a[1] != shape_b[0]:
-        raise RuntimeError(f"Tensors common dim must match,but {shape_a[1]} and {shape_b[0]}")
+        # the reference's message prints a.shape(0) and b.shape(0) here (src/ops.cpp:555); kept verbatim
+        raise RuntimeError(f"Tensors common dim must match,but {shape_a[0]} and {shape_b[0]}")
     return 1, int(shape_a[0]), int(shape_a[1]), int(shape_b[1])
 
 

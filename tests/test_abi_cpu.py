@@ -1,0 +1,112 @@
+"""CPU-side checks of the C-ABI library: it builds, loads, exports every symbol that
+include/tvb.h declares, and its host-only entry points behave.  No compute call is made."""
+import ctypes as C
+import re
+import shutil
+import subprocess
+from pathlib import Path
+
+import pytest
+
+import refcheck as R
+
+ROOT = Path(__file__).resolve().parent.parent
+HEADER = ROOT / "include" / "tvb.h"
+
+
+def declared_symbols():
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return sorted(set(re.findall(r"\b(tvb_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported_and_bound(tv):
+    from tensorvia_b200 import _lib
+    names = declared_symbols()
+    assert len(names) >= 25
+    raw = C.CDLL(str(_lib.LIB_PATH))
+    for n in names:
+        getattr(raw, n)  # raises AttributeError if the library does not export it
+    assert sorted(_lib.SIGNATURES) == names, "ctypes binding and header disagree"
+
+
+def test_header_compiles_as_plain_c(tmp_path):
+    src = tmp_path / "t.c"
+    src.write_text('#include "tvb.h"\nint main(void){ tvb_plan_info p; (void)p; return TVB_OK; }\n')
+    subprocess.run([shutil.which("gcc") or "gcc", "-std=c99", "-Wall", "-Werror", "-pedantic", f"-I{ROOT / 'include'}",
+                    "-c", str(src), "-o", str(tmp_path / "t.o")], check=True)
+
+
+def test_dtype_rules_without_a_gpu(tv):
+    lib = tv._lib.lib
+    table = [[lib.tvb_compute_type(a, b) for b in range(8)] for a in range(8)]
+    assert table == [[R.oracle().tvo_compute_type(a, b) for b in range(8)] for a in range(8)]
+    assert lib.tvb_compute_type(-1, 0) == -1 and lib.tvb_compute_type(0, 8) == -1
+    assert [lib.tvb_dtype_size(d) for d in range(8)] == [1, 2, 4, 8, 2, 2, 4, 8]
+    assert lib.tvb_dtype_size(9) == 0
+
+
+def test_calls_fail_loudly_without_a_device(tv):
+    """On a machine without a GPU the library reports errors; it never computes on the CPU."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    lib = tv._lib.lib
+    assert lib.tvb_init(0) == 8  # TVB_ERR_NO_DEVICE
+    assert b"no CUDA device" in lib.tvb_last_error_string()
+    p = C.c_void_p()
+    assert lib.tvb_malloc(0, 1024, C.byref(p)) == 6  # TVB_ERR_NOT_INIT
+    assert lib.tvb_matmul(0, 1, 1, 1, 6, 6, 6, 1, 2, 2, 2, None) == 6
+    assert lib.tvb_sync(0) == 6
+    assert lib.tvb_init(-1) == 1 and lib.tvb_init(64) == 1
+    with pytest.raises(tv._lib.TvbError):
+        tv.ops.init(0)
+
+
+def test_shard_range(tv):
+    sr = tv.ops.shard_range
+    # configuration 5: 65536 rows over 1/2/4/8 GPUs, cut on 128-row tiles
+    for parts in (1, 2, 4, 8):
+        spans = [sr(65536, 128, parts, i) for i in range(parts)]
+        assert all(c == 65536 // parts for _, c in spans)
+        assert [b for b, _ in spans] == [i * 65536 // parts for i in range(parts)]
+    # ragged: covers everything exactly once, in order, on granule boundaries
+    for units, granule, parts in ((1000, 128, 3), (2592, 128, 8), (5, 128, 4), (32, 1, 8), (7, 1, 8), (1, 1, 3)):
+        spans = [sr(units, granule, parts, i) for i in range(parts)]
+        pos = 0
+        for b, c in spans:
+            assert b == pos and c >= 0 and (b % granule == 0 or c == 0)
+            pos += c
+        assert pos == units
+        sizes = [c for _, c in spans]
+        assert max(sizes) - min(sizes) < 2 * granule
+    lib = tv._lib.lib
+    b, c = C.c_int64(), C.c_int64()
+    assert lib.tvb_shard_range(10, 0, 2, 0, C.byref(b), C.byref(c)) == 1
+    assert lib.tvb_shard_range(10, 1, 2, 2, C.byref(b), C.byref(c)) == 1
+    assert lib.tvb_shard_range(10, 1, 2, 0, None, C.byref(c)) == 1
+
+
+def test_option_setters_validate(tv):
+    lib = tv._lib.lib
+    assert lib.tvb_set_wait_limit_ms(0) == 1 and lib.tvb_set_wait_limit_ms(2000) == 0
+    assert lib.tvb_set_fp32_mode(5) == 1 and lib.tvb_set_fp32_mode(0) == 0
+    assert lib.tvb_kernel_launches() == 0 or lib.tvb_kernel_launches() > 0
+    assert b"sm_100a" in lib.tvb_version()
+
+
+def test_block_pool_unit(tmp_path):
+    exe = tmp_path / "test_block_pool"
+    subprocess.run([shutil.which("g++") or "g++", "-std=c++17", "-O1", "-fsanitize=address,undefined",
+                    f"-I{ROOT / 'tensorvia_b200' / 'csrc'}", str(ROOT / "tests" / "cpp" / "test_block_pool.cpp"),
+                    "-o", str(exe)], check=True)
+    out = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert out.returncode == 0, out.stdout + out.stderr
+    assert "all checks passed" in out.stdout
+
+
+def test_oracle_is_not_reachable_from_the_product():
+    """Nothing under tensorvia_b200/ or include/ may import, link or run the oracle."""
+    for path in list((ROOT / "tensorvia_b200").rglob("*")) + list((ROOT / "include").rglob("*")):
+        if path.is_file() and path.suffix in {".py", ".cu", ".cuh", ".h", ".cpp", ".hpp"}:
+            text = path.read_text(errors="ignore")
+            assert "oracle" not in text.lower() and "refcheck" not in text, path
