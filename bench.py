@@ -1,0 +1,403 @@
+#!/usr/bin/env python
+"""Benchmark of the matmul operator on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config c1..c5] [--impl reference]
+
+A step is one ops::matmul over one set of synthetic operands that already sit in HBM.
+The default workload is configuration 2 of the baseline: bf16 A[4096,4096] @ B[4096,4096],
+fp32 accumulation, bf16 result.  With N > 1 (launched by torch.distributed.run, one rank per
+GPU) every rank multiplies its own 4096-row slab of a [N*4096, 4096] A by a replicated B
+(weak scaling, no collective in the timed region; B is broadcast once before it).
+
+Prints ONE JSON line (rank 0).  `value` is the whole-job TFLOP/s over the timed steps
+(CUDA events on the launch stream, max over ranks).  `e2e` is the same metric through the
+host-buffer entry point tvb_matmul_host: pinned host operands in, result out, copies inside
+the timed region.  `roofline` relates the kernel to the measured cuBLAS bf16 peak of this
+pool; `cpu_baseline` is the reference's own CPU/OpenMP ops::Mul timed on this box's cores.
+
+`--impl reference` times the reference's CPU implementation (oracle/_ref, built from the
+reference's own sources; else the C restatement in oracle/) on a bounded sample of the same
+workload and prints the same line shape with "impl": "reference".
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+INT8, BF16, F16, F32 = 0, 4, 5, 6
+SEED_BASE = 0x5EED0000
+# name: (config number, dtype, batch or None, M, K, N, dist, element size)
+CONFIGS = {
+    "c1": (1, F32, None, 2592, 2048, 4096, 0, 4),
+    "c2": (2, BF16, None, 4096, 4096, 4096, 0, 2),
+    "c3": (3, F16, 32, 1024, 4096, 1024, 0, 2),
+    "c4": (4, INT8, None, 8192, 8192, 8192, 1, 1),
+    "c5": (5, F32, None, 65536, 4096, 4096, 0, 4),
+}
+DTYPE_NAME = {INT8: "int8", BF16: "bf16", F16: "fp16", F32: "fp32"}
+WORKLOAD_TEXT = {
+    "c1": "fp32 A[2592,2048] @ B[2048,4096] -> fp32 (3xTF32 on tcgen05)",
+    "c2": "bf16 A[4096,4096] @ B[4096,4096] -> bf16, fp32 accumulate",
+    "c3": "fp16 batched A[32,1024,4096] @ B[32,4096,1024] -> fp16, fp32 accumulate",
+    "c4": "int8 A[8192,8192] @ B[8192,8192] -> int8 (s32 accumulate, low byte)",
+    "c5": "fp32 A[65536,4096] @ B[4096,4096] -> fp32 (3xTF32 on tcgen05)",
+}
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the
+# ncu captures summarised under profiles/ (None until a capture exists for the workload)
+NCU_TRAFFIC_BYTES = {"c2": None}
+L2_BYTES = 126 * 1024 * 1024
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"bf16_burst": float(d["bf16_tflops"]), "bf16_sustained": float(d["bf16_tflops_sustained"]),
+                "hbm_gbs": float(d["hbm_gbs"]), "source": "measured"}
+    return {"bf16_burst": 1590.0, "bf16_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler(threading.Thread):
+    """Polls NVML (read-only) for SM clock and throttle reasons while the timed region runs."""
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._halt = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+            self.ok = True
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        names = {"hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+                 "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+                 "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+                 "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4)}
+        while not self._halt.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                try:
+                    r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def stop(self):
+        self._halt.set()
+        self.join(timeout=2)
+        s = sorted(self.samples)
+        return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+def physical_gpu_index(local: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+    if vis:
+        parts = [v for v in vis.split(",") if v.strip() != ""]
+        if local < len(parts) and parts[local].strip().isdigit():
+            return int(parts[local])
+    return local
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU arm: the reference's own ops::Mul (or the C restatement) on host cores
+# ---------------------------------------------------------------------------------------------
+def load_cpu_impl():
+    """-> (kind, matmul(a, b, dtype) -> seconds, threads).  Test infrastructure under oracle/ is
+    executed here, and only here, as the CPU baseline."""
+    sys.path.insert(0, str(ROOT / "tests"))
+    import refcheck as R
+    if R.have_ref():
+        lib = R.ref()
+
+        def run(a, b, dt):
+            t0 = time.perf_counter()
+            R.ref_matmul(a, dt, b, dt)
+            return time.perf_counter() - t0
+        return "reference", run, int(lib.tvref_threads()), R
+
+    def run(a, b, dt):
+        t0 = time.perf_counter()
+        R.oracle_matmul(a, dt, b, dt, "cpu")
+        return time.perf_counter() - t0
+    return "port", run, int(R.oracle().tvo_threads()), R
+
+
+def cpu_sample(R, cfg_name: str, rows: int):
+    """Operands of a bounded sample: the first `rows` rows of A (of the first batches) with the
+    whole B, regenerated from the configuration's seeds."""
+    cfg, dt, batch, M, K, N, dist, es = CONFIGS[cfg_name]
+    seed_a, seed_b = SEED_BASE + 2 * cfg, SEED_BASE + 2 * cfg + 1
+    if batch is None:
+        rows = min(rows, M)
+        a = R.fill((rows, K), dt, seed_a, dist)
+        b = R.fill((K, N), dt, seed_b, dist)
+        return a, b, 2.0 * rows * K * N, f"first {rows} of {M} rows of A, whole B"
+    nb = max(1, min(batch, rows // M))
+    a = R.fill((nb, M, K), dt, seed_a, dist)
+    b = R.fill((nb, K, N), dt, seed_b, dist)
+    return a, b, 2.0 * nb * M * K * N, f"first {nb} of {batch} batches"
+
+
+def reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0  # the CPU arm runs on rank 0 alone
+    kind, run, threads, R = load_cpu_impl()
+    cfg_name = args.config
+    cfg, dt, batch, M, K, N, dist, es = CONFIGS[cfg_name]
+    # size one step so that (steps + warmup) of them end within ~2 minutes: calibrate on the
+    # smallest sample that still takes the reference's large-output path (>= 1 Mi outputs)
+    budget = 120.0 / max(1, args.steps + args.warmup)
+    if batch is None:
+        min_rows = -(-max(64, -(-1024 * 1024 // N)) // 64) * 64
+        a, b, flops, _ = cpu_sample(R, cfg_name, min_rows)
+        t_probe = max(run(a, b, dt), 1e-3)
+        rows = min(M, max(min_rows, int(min_rows * budget / t_probe) // 64 * 64))
+    else:
+        a, b, flops, _ = cpu_sample(R, cfg_name, M)          # one batch
+        t_probe = max(run(a, b, dt), 1e-3)
+        rows = M * min(batch, max(1, int(budget / t_probe)))
+    a, b, flops, sample = cpu_sample(R, cfg_name, rows)
+    for _ in range(args.warmup):
+        run(a, b, dt)
+    t = 0.0
+    for _ in range(args.steps):
+        t += run(a, b, dt)
+    per = t / max(1, args.steps)
+    val = flops / per / 1e12
+    unit = "TOP/s" if dt == INT8 else "TFLOP/s"
+    line = {
+        "impl": "reference", "metric": "ops::matmul TFLOP/s", "value": val, "unit": unit, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": per * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": DTYPE_NAME[dt], "data": "synthetic",
+        "config": {"workload": WORKLOAD_TEXT[cfg_name], "config": cfg_name,
+                   "note": "reference CPU/OpenMP ops::Mul on host cores; each step is a bounded sample"},
+        "cpu_baseline": {"value": val, "unit": unit, "cores": threads, "kind": kind, "sample": sample},
+        "e2e": {"value": val, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------
+def gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.cuda.set_device(local)
+
+    from tensorvia_b200 import _lib, ops   # raises if the CUDA library is missing
+    lib, check = _lib.lib, _lib.check
+    ops.init(local)
+
+    cfg_name = args.config
+    cfg, dt, batch, M, K, N, dist_kind, es = CONFIGS[cfg_name]
+    nb = batch or 1
+    seed_a, seed_b = SEED_BASE + 2 * cfg, SEED_BASE + 2 * cfg + 1
+    bytes_a, bytes_b, bytes_c = nb * M * K * es, nb * K * N * es, nb * M * N * es
+    flops_rank = 2.0 * nb * M * K * N
+
+    # Rotating operand sets: successive steps touch different buffers, so that together they
+    # exceed the L2 and no step finds its operands cached from the previous one.
+    per_set = bytes_a + bytes_b + bytes_c
+    nsets = max(2, -(-3 * L2_BYTES // per_set)) if per_set < 3 * L2_BYTES else 1
+    stream = torch.cuda.current_stream().cuda_stream or 1   # 1 = CUDA's handle of the legacy default stream
+    sp = C.c_void_p(stream)
+
+    def dalloc(n):
+        p = C.c_void_p()
+        check(lib.tvb_malloc(local, n, C.byref(p)))
+        return p.value
+
+    sets = []
+    for s in range(nsets):
+        pa, pb, pc = dalloc(bytes_a), dalloc(bytes_b), dalloc(bytes_c)
+        # rank r owns rows [r*M, (r+1)*M) of the global A (2-D) or its own run of batches (3-D)
+        first_a = rank * nb * M * K
+        check(lib.tvb_fill_splitmix(local, pa, dt, nb * M * K, seed_a + 16 * s, first_a, dist_kind, sp))
+        first_b = rank * nb * K * N if batch else 0
+        check(lib.tvb_fill_splitmix(local, pb, dt, nb * K * N, seed_b + 16 * s, first_b, dist_kind, sp))
+        sets.append((pa, pb, pc))
+    torch.cuda.synchronize()
+    if world > 1 and batch is None:
+        # "B is broadcast once": rank 0's copy goes to every rank over NCCL, outside the timed region
+        for (pa, pb, pc) in sets:
+            tb = torch.empty(bytes_b, dtype=torch.uint8, device="cuda")
+            check(lib.tvb_memcpy_d2d(local, tb.data_ptr(), pb, bytes_b, sp))
+            dist.broadcast(tb, src=0)
+            check(lib.tvb_memcpy_d2d(local, pb, tb.data_ptr(), bytes_b, sp))
+        torch.cuda.synchronize()
+
+    dtc = lib.tvb_compute_type(dt, dt)
+
+    def step(i):
+        pa, pb, pc = sets[i % nsets]
+        check(lib.tvb_matmul(local, pa, pb, pc, dt, dt, dtc, nb, M, K, N, sp))
+
+    for i in range(max(3, args.warmup)):
+        step(i)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(physical_gpu_index(local))
+    sampler.start()
+    launches0 = lib.tvb_kernel_launches()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for i in range(args.steps):
+        step(i)
+    ev1.record()
+    torch.cuda.synchronize()
+    launches = lib.tvb_kernel_launches() - launches0
+    clocks = sampler.stop()
+    if world > 1:
+        dist.barrier()
+    check(lib.tvb_sync(local))  # also surfaces a timed-out device wait
+    ms_total = ev0.elapsed_time(ev1)
+
+    # ---- end to end through the host-buffer entry point ---------------------------------------
+    ha, hb, hc = C.c_void_p(), C.c_void_p(), C.c_void_p()
+    check(lib.tvb_host_alloc(bytes_a, C.byref(ha)))
+    check(lib.tvb_host_alloc(bytes_b, C.byref(hb)))
+    check(lib.tvb_host_alloc(bytes_c, C.byref(hc)))
+    check(lib.tvb_memcpy_d2h(local, ha, sets[0][0], bytes_a, None))
+    check(lib.tvb_memcpy_d2h(local, hb, sets[0][1], bytes_b, None))
+    check(lib.tvb_sync(local))
+    e2e_steps = max(3, min(args.steps, 50))
+    for _ in range(2):
+        check(lib.tvb_matmul_host(local, ha, hb, hc, dt, dt, dtc, nb, M, K, N))
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        check(lib.tvb_matmul_host(local, ha, hb, hc, dt, dt, dtc, nb, M, K, N))
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    # the result the caller got back equals the device-resident result of the same operands
+    import numpy as np
+    host_c = np.frombuffer((C.c_char * min(bytes_c, 1 << 20)).from_address(hc.value), dtype=np.uint8)
+    dev_c = np.empty_like(host_c)
+    check(lib.tvb_matmul(local, sets[0][0], sets[0][1], sets[0][2], dt, dt, dtc, nb, M, K, N, None))
+    check(lib.tvb_memcpy_d2h(local, dev_c.ctypes.data, sets[0][2], dev_c.nbytes, None))
+    check(lib.tvb_sync(local))
+    e2e_same = bool((host_c == dev_c).all())
+    for p in (ha, hb, hc):
+        check(lib.tvb_host_free(p))
+
+    # ---- max over ranks ---------------------------------------------------------------------------
+    if world > 1:
+        t = torch.tensor([ms_total, e2e_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total, e2e_ms = float(t[0]), float(t[1])
+    ms_step = ms_total / args.steps
+    value = world * flops_rank / (ms_step * 1e-3) / 1e12
+    e2e_value = world * flops_rank / (e2e_ms * 1e-3) / 1e12
+
+    if rank == 0:
+        peaks = measured_peaks()
+        info = ops.plan(dt, dt, nb, M, K, N, device=local)
+        long_run = ms_total > 1000.0
+        if dt in (BF16, F16):
+            peak, peak_name = (peaks["bf16_sustained"], "bf16_tflops_sustained") if long_run else (peaks["bf16_burst"], "bf16_tflops")
+        elif dt == INT8:
+            peak, peak_name = 2.0 * (peaks["bf16_sustained"] if long_run else peaks["bf16_burst"]), "2 x bf16_tflops (int8 runs at twice the bf16 rate; no int8 figure was measured)"
+        else:
+            peak, peak_name = 0.5 * (peaks["bf16_sustained"] if long_run else peaks["bf16_burst"]) / 3.0, "bf16_tflops / 2 / 3 (tf32 runs at half the bf16 rate, three passes per product)"
+        achieved = flops_rank / (ms_step * 1e-3) / 1e12
+        unit = "TOP/s" if dt == INT8 else "TFLOP/s"
+        line = {
+            "metric": "ops::matmul TFLOP/s", "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": DTYPE_NAME[dt], "data": "synthetic",
+            "config": {
+                "workload": WORKLOAD_TEXT[cfg_name], "config": cfg_name, "per_gpu": "one full problem per GPU" if world > 1 else "single GPU",
+                "parallelism": ("rows of A sharded, B replicated" if batch is None else "batches sharded") if world > 1 else "none",
+                "kernel": f"tcgen05 {info.tile_m}x{info.tile_n}x{info.tile_k}, {info.stages} stages, {info.ctas} CTAs, {info.passes} pass(es)" if info.algo == 1 else "simt",
+                "l2": f"{nsets} rotating operand sets ({nsets * per_set >> 20} MiB) exceed the {L2_BYTES >> 20} MiB L2",
+                "inputs": "SplitMix64 counter-based, seeds 0x5EED0000+2*cfg (A), +1 (B)",
+            },
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
+                         "traffic": NCU_TRAFFIC_BYTES.get(cfg_name), "peak_source": f"{peaks['source']}: {peak_name}",
+                         "flops_per_launch": flops_rank, "frac_of_nominal_2250": (achieved / 2250.0) if dt in (BF16, F16) else None},
+            "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": bytes_a + bytes_b, "d2h_bytes_per_step": bytes_c,
+                    "ms_per_step": e2e_ms, "steps": e2e_steps, "result_equals_device_path": e2e_same,
+                    "api": "tvb_matmul_host (pinned host buffers)"},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            try:
+                kind, run, threads, R = load_cpu_impl()
+                rows = M if batch is None else nb * M
+                if cfg_name in ("c4", "c5"):
+                    rows = 1024
+                a, b, fl, sample = cpu_sample(R, cfg_name, rows)
+                t = run(a, b, dt)
+                line["cpu_baseline"] = {"value": fl / t / 1e12, "unit": unit, "cores": threads, "kind": kind,
+                                        "sample": sample + f", 1 run, {t:.2f} s", "host_cpus": os.cpu_count()}
+            except Exception as e:  # the baseline must never take the GPU line down
+                line["cpu_baseline"] = {"value": None, "unit": unit, "cores": 0, "kind": "unavailable", "sample": str(e)[:200]}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--config", default="c2", choices=sorted(CONFIGS))
+    ap.add_argument("--impl", default="tensorvia_b200", choices=["tensorvia_b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+    if args.gpus > 1 and "WORLD_SIZE" not in os.environ:
+        # convenience: relaunch under torch.distributed.run, one rank per GPU
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", "29531", __file__] + sys.argv[1:]
+        return subprocess.call(cmd)
+    return gpu_arm(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -163,6 +163,10 @@ int tvb_set_fp32_mode(int mode);
 /* The split the fp32 path applies to its operands: hi = tf32(x), lo = tf32(x - hi),
  * `count` floats each; all three pointers 16-byte aligned device memory. */
 int tvb_split_tf32(int device, const void* src, void* hi, void* lo, uint64_t count, void* stream);
+/* Failure-path self test: launches one small kernel whose only wait can never be satisfied
+ * (an mbarrier nothing arrives on), lets the wait run out after `limit_ms` and returns what
+ * tvb_sync then reports: TVB_ERR_KERNEL_TIMEOUT.  No fault, no hang; the context stays usable. */
+int tvb_selftest_wait_timeout(int device, uint32_t limit_ms);
 /* Number of kernels this library has launched since load (all devices). */
 uint64_t tvb_kernel_launches(void);
 /* Upper bound, in milliseconds, on any device-side wait (default 2000). */

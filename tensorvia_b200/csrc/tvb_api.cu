@@ -458,6 +458,18 @@ int tvb_split_tf32(int device, const void* src, void* hi, void* lo, uint64_t cou
   return TVB_OK;
 }
 
+int tvb_selftest_wait_timeout(int device, uint32_t limit_ms) {
+  Context* c = nullptr;
+  int rc = get_ctx(device, &c);
+  if (rc != TVB_OK) return rc;
+  if (limit_ms == 0 || limit_ms > 2000) return fail(TVB_ERR_INVALID_ARG, "limit must be 1..2000 ms");
+  DeviceGuard guard(device);
+  wait_timeout_probe_kernel<<<1, 32, 0, c->stream>>>(c->d_status, static_cast<uint64_t>(limit_ms) * 1000000ull);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  TVB_CUDA(cudaGetLastError());
+  return tvb_sync(device);
+}
+
 int tvb_device_count(int* count) {
   if (!count) return fail(TVB_ERR_INVALID_ARG, "count is null");
   int n = 0;

@@ -1,0 +1,101 @@
+"""Helpers for the GPU tests: everything goes through the C ABI (ctypes), with device memory
+from the library's own pool — torch is not involved."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+import refcheck as R
+
+
+class Dev:
+    """Thin RAII-ish wrapper over tvb_malloc / tvb_memcpy for numpy arrays."""
+
+    def __init__(self, tv, device: int = 0):
+        self.tv = tv
+        self.lib = tv._lib.lib
+        self.check = tv._lib.check
+        self.device = device
+        tv.ops.init(device)
+        self._live = []
+
+    def alloc(self, nbytes: int) -> int:
+        p = C.c_void_p()
+        self.check(self.lib.tvb_malloc(self.device, max(1, nbytes), C.byref(p)))
+        self._live.append(p.value)
+        return p.value
+
+    def free(self, ptr: int) -> None:
+        self.check(self.lib.tvb_free(self.device, ptr))
+        self._live.remove(ptr)
+
+    def free_all(self) -> None:
+        self.check(self.lib.tvb_sync(self.device))
+        for p in list(self._live):
+            self.free(p)
+
+    def upload(self, arr: np.ndarray) -> int:
+        arr = np.ascontiguousarray(arr)
+        p = self.alloc(arr.nbytes)
+        self.check(self.lib.tvb_memcpy_h2d(self.device, p, arr.ctypes.data, arr.nbytes, None))
+        self.check(self.lib.tvb_sync(self.device))  # arr may be a temporary
+        return p
+
+    def download(self, ptr: int, shape, dtype: int, offset_bytes: int = 0) -> np.ndarray:
+        out = np.empty(shape, dtype=R.NP[dtype])
+        self.check(self.lib.tvb_memcpy_d2h(self.device, out.ctypes.data, ptr + offset_bytes, out.nbytes, None))
+        self.check(self.lib.tvb_sync(self.device))
+        return out
+
+    def fill(self, shape, dtype: int, seed: int, dist: int = 0, first: int = 0) -> int:
+        n = int(np.prod(shape))
+        p = self.alloc(n * R.NP[dtype]().itemsize)
+        self.check(self.lib.tvb_fill_splitmix(self.device, p, dtype, n, seed, first, dist, None))
+        return p
+
+    def matmul_ptr(self, pa, dta, pb, dtb, pc, batch, M, K, N, algo=0) -> None:
+        dtc = self.lib.tvb_compute_type(dta, dtb)
+        self.check(self.lib.tvb_matmul_algo(self.device, pa, pb, pc, dta, dtb, dtc, batch, M, K, N, None, algo))
+
+    def sync(self) -> None:
+        self.check(self.lib.tvb_sync(self.device))
+
+    def matmul(self, a: np.ndarray, dta: int, b: np.ndarray, dtb: int, algo: int = 0):
+        """Host arrays in, host array out, through device buffers and tvb_matmul_algo."""
+        batch, M, K, N = R.bmkn(a.shape, b.shape)
+        dtc = self.lib.tvb_compute_type(dta, dtb)
+        shape_c = (batch, M, N) if a.ndim == 3 else (M, N)
+        pa, pb = self.upload(a), self.upload(b)
+        nbytes = int(np.prod(shape_c)) * R.NP[dtc]().itemsize
+        # guard bands around C: a kernel that writes outside its output is caught here
+        guard = 256
+        praw = self.alloc(nbytes + 2 * guard)
+        canary = np.full(nbytes + 2 * guard, 0xA5, dtype=np.uint8)
+        self.check(self.lib.tvb_memcpy_h2d(self.device, praw, canary.ctypes.data, canary.nbytes, None))
+        self.sync()
+        try:
+            self.matmul_ptr(pa, dta, pb, dtb, praw + guard, batch, M, K, N, algo)
+            self.sync()
+            whole = self.download(praw, (nbytes + 2 * guard,), R.INT8).view(np.uint8)
+            assert (whole[:guard] == 0xA5).all() and (whole[-guard:] == 0xA5).all(), "write outside C"
+            c = whole[guard:guard + nbytes].copy().view(R.NP[dtc]).reshape(shape_c)
+        finally:
+            for p in (pa, pb, praw):
+                self.free(p)
+        return c, dtc
+
+
+def assert_matches(c, dtc, expect, dte, tol_f32=1e-5, tol_half=1e-2, tol_f64=1e-12, what=""):
+    """Bit-exact for integer results; relative Frobenius error within the tolerance for floats:
+    1e-5 for fp32 results, 1e-2 for fp16/bf16 results (fp32 accumulation), 1e-12 for fp64."""
+    assert dtc == dte, f"{what}: result dtype {dtc} != expected {dte}"
+    assert c.shape == expect.shape, f"{what}: shape {c.shape} != {expect.shape}"
+    if dtc <= R.INT64:
+        bad = int((c != expect).sum())
+        assert bad == 0, f"{what}: {bad} of {c.size} integer outputs differ"
+        return 0.0
+    err = R.rel_frobenius(c, expect, dtc)
+    tol = {R.BFLOAT16: tol_half, R.FLOAT16: tol_half, R.FLOAT32: tol_f32, R.FLOAT64: tol_f64}[dtc]
+    assert err <= tol, f"{what}: relative Frobenius error {err:.3e} > {tol:g}"
+    return err

@@ -11,7 +11,9 @@ from __future__ import annotations
 
 import ctypes as C
 import hashlib
+import os
 import subprocess
+import sys
 from pathlib import Path
 
 import numpy as np
@@ -73,7 +75,18 @@ def have_ref() -> bool:
 def ref() -> C.CDLL:
     global _ref
     if _ref is None:
-        lib = C.CDLL(str(REF_LIB))
+        # the reference prints a registration banner to stdout from a static initialiser
+        # (src/factory.cpp:19, src/init.cpp:13); keep it off the caller's stdout
+        sys.stdout.flush()
+        saved = os.dup(1)
+        devnull = os.open(os.devnull, os.O_WRONLY)
+        try:
+            os.dup2(devnull, 1)
+            lib = C.CDLL(str(REF_LIB))
+        finally:
+            os.dup2(saved, 1)
+            os.close(saved)
+            os.close(devnull)
         i64p = C.POINTER(C.c_int64)
         lib.tvref_mul.restype = C.c_int
         lib.tvref_mul.argtypes = [C.c_void_p, C.c_int, C.c_int, i64p, C.c_void_p, C.c_int, C.c_int, i64p,

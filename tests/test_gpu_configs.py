@@ -1,0 +1,259 @@
+"""The five benchmark configurations at FULL size on the GPU, checked against rows of the
+reference's own output (golden_configs.npz) and through size-independent properties;
+plus the C ABI's error behaviour, storage pool, end-to-end host call, seeded generator,
+bounded-wait failure path and the sharded decomposition (emulated on one device)."""
+import ctypes as C
+import json
+
+import numpy as np
+import pytest
+
+import refcheck as R
+from gpuutil import Dev, assert_matches
+
+pytestmark = pytest.mark.gpu
+
+META = json.loads((R.GOLDEN_DIR / "golden_meta.json").read_text())
+GOLD = np.load(R.GOLDEN_DIR / "golden_configs.npz")
+AUTO, TCGEN05, SIMT = 0, 1, 2
+
+
+@pytest.fixture(scope="module")
+def dev(tv):
+    d = Dev(tv)
+    yield d
+    d.free_all()
+
+
+def _run_config(dev, cfg):
+    m = META["configs"][str(cfg)]
+    dt, batch, M, K, N, dist = m["dtype"], m["batch"], m["M"], m["K"], m["N"], m["dist"]
+    nb = batch or 1
+    es = R.NP[dt]().itemsize
+    pa = dev.fill((nb, M, K), dt, m["seed_a"], dist)
+    pb = dev.fill((nb, K, N), dt, m["seed_b"], dist)
+    pc = dev.alloc(nb * M * N * es)
+    dev.matmul_ptr(pa, dt, pb, dt, pc, nb, M, K, N)
+    dev.sync()
+    return m, pa, pb, pc, es
+
+
+@pytest.mark.parametrize("cfg", [1, 2, 3, 4, 5])
+def test_config_full_size_against_reference_rows(dev, cfg):
+    m, pa, pb, pc, es = _run_config(dev, cfg)
+    dt, M, K, N = m["dtype"], m["M"], m["K"], m["N"]
+    try:
+        # the device generator made the same A rows the reference was fed
+        kept = [tuple(p) for p in m["kept"]]
+        a_rows = np.stack([dev.download(pa, (K,), dt, offset_bytes=(b * M + r) * K * es) for b, r in kept])
+        assert R.sha(a_rows) == m["sha_a_rows"], "device-generated inputs differ from the reference's inputs"
+        got = np.stack([dev.download(pc, (N,), dt, offset_bytes=(b * M + r) * N * es) for b, r in kept])
+        exp, dte = R.cuda_expected_from_cpu(GOLD[f"c{cfg}_rows"], m["dtc_cpu"], dt, dt)
+        err = assert_matches(got, dt, exp, dte, what=f"config {cfg}")
+        print(f"config {cfg}: relative Frobenius error vs reference rows = {err:.3e}")
+    finally:
+        for p in (pa, pb, pc):
+            dev.free(p)
+
+
+@pytest.mark.parametrize("cfg", [2, 4, 5])
+def test_config_row_slab_equals_full_run(dev, cfg):
+    """Sharding property at full size: a slab of A's rows multiplied alone gives, bit for bit,
+    the same rows as the whole product (K is never split; tiles are computed independently)."""
+    m, pa, pb, pc, es = _run_config(dev, cfg)
+    dt, M, K, N = m["dtype"], m["M"], m["K"], m["N"]
+    try:
+        for parts, idx in ((8, 3), (4, 3)):
+            begin, count = dev.tv.ops.shard_range(M, 128, parts, idx)
+            pslab = dev.alloc(count * N * es)
+            dev.matmul_ptr(pa + begin * K * es, dt, pb, dt, pslab, 1, count, K, N)
+            dev.sync()
+            step = max(1, count // 64)
+            for r in list(range(0, count, step))[:64]:
+                full = dev.download(pc, (N,), dt, offset_bytes=(begin + r) * N * es)
+                slab = dev.download(pslab, (N,), dt, offset_bytes=r * N * es)
+                assert full.tobytes() == slab.tobytes()
+            dev.free(pslab)
+    finally:
+        for p in (pa, pb, pc):
+            dev.free(p)
+
+
+def test_config3_batch_slab_equals_full_run(dev):
+    m, pa, pb, pc, es = _run_config(dev, 3)
+    dt, batch, M, K, N = m["dtype"], m["batch"], m["M"], m["K"], m["N"]
+    try:
+        begin, count = dev.tv.ops.shard_range(batch, 1, 8, 5)
+        assert count == 4
+        pslab = dev.alloc(count * M * N * es)
+        dev.matmul_ptr(pa + begin * M * K * es, dt, pb + begin * K * N * es, dt, pslab, count, M, K, N)
+        dev.sync()
+        full = dev.download(pc, (count, M, N), dt, offset_bytes=begin * M * N * es)
+        slab = dev.download(pslab, (count, M, N), dt)
+        assert full.tobytes() == slab.tobytes()
+        dev.free(pslab)
+    finally:
+        for p in (pa, pb, pc):
+            dev.free(p)
+
+
+def test_int8_full_size_linearity_and_identity(dev):
+    """8192^3 int8: A @ I == A exactly, and A @ (B1 + B2) == A @ B1 + A @ B2 modulo 2^8."""
+    n = 8192
+    pa = dev.fill((n, n), R.INT8, 77, 1)
+    eye = np.eye(n, dtype=np.int8)
+    pi = dev.upload(eye)
+    pc = dev.alloc(n * n)
+    dev.matmul_ptr(pa, R.INT8, pi, R.INT8, pc, 1, n, n, n)
+    dev.sync()
+    a = dev.download(pa, (n, n), R.INT8); c = dev.download(pc, (n, n), R.INT8)
+    assert (a == c).all()
+    b1 = R.fill((n, n), R.INT8, 78, 1); b2 = R.fill((n, n), R.INT8, 79, 1)
+    p1, p2, p12 = dev.upload(b1), dev.upload(b2), dev.upload((b1 + b2).astype(np.int8))
+    c1, c2, c12 = dev.alloc(n * n), dev.alloc(n * n), dev.alloc(n * n)
+    for pb_, pc_ in ((p1, c1), (p2, c2), (p12, c12)):
+        dev.matmul_ptr(pa, R.INT8, pb_, R.INT8, pc_, 1, n, n, n)
+    dev.sync()
+    r1, r2, r12 = (dev.download(p, (n, n), R.INT8) for p in (c1, c2, c12))
+    assert ((r1.astype(np.int16) + r2.astype(np.int16)).astype(np.int8) == r12).all()
+    for p in (pa, pi, pc, p1, p2, p12, c1, c2, c12):
+        dev.free(p)
+
+
+# ---- C ABI behaviour ---------------------------------------------------------------------------------
+def test_error_codes(dev, tv):
+    lib = tv._lib.lib
+    p = dev.alloc(4096)
+    f32 = R.FLOAT32
+    assert lib.tvb_matmul(0, None, p, p, f32, f32, f32, 1, 4, 4, 4, None) == 1          # null pointer
+    assert lib.tvb_matmul(0, p, p, p, 9, f32, f32, 1, 4, 4, 4, None) == 3               # bad dtype
+    assert lib.tvb_matmul(0, p, p, p, f32, f32, R.FLOAT64, 1, 4, 4, 4, None) == 3       # wrong result dtype
+    assert lib.tvb_matmul(0, p, p, p, R.BFLOAT16, R.BFLOAT16, f32, 1, 4, 4, 4, None) == 3
+    assert lib.tvb_matmul(0, p, p, p, f32, f32, f32, 1, 0, 4, 4, None) == 2             # empty dimension
+    assert lib.tvb_matmul(0, p, p, p, f32, f32, f32, -1, 4, 4, 4, None) == 2
+    assert lib.tvb_matmul(5, p, p, p, f32, f32, f32, 1, 4, 4, 4, None) == 6             # device not initialised
+    assert lib.tvb_matmul_algo(0, p, p, p, f32, f32, f32, 1, 4, 4, 4, None, 7) == 1     # bad algo
+    assert lib.tvb_matmul_algo(0, p, p, p, R.INT16, R.INT16, R.INT16, 1, 4, 4, 4, None, 1) == 9
+    assert b"tcgen05" in lib.tvb_last_error_string()
+    assert lib.tvb_free(0, 12345) == 1
+    dev.free(p)
+    dev.sync()  # none of the failed calls left an error behind
+
+
+def test_pool_reuses_blocks_and_host_call_matches_device_call(dev, tv):
+    lib = tv._lib.lib
+    A = R.fill((500, 256), R.BFLOAT16, 1); B = R.fill((256, 384), R.BFLOAT16, 2)
+    first = tv.ops.matmul_host(A, B, R.BFLOAT16, R.BFLOAT16)
+    st0 = tv._lib.PoolStats(); lib.tvb_pool_get_stats(0, C.byref(st0))
+    for _ in range(20):
+        again = tv.ops.matmul_host(A, B, R.BFLOAT16, R.BFLOAT16)
+    st1 = tv._lib.PoolStats(); lib.tvb_pool_get_stats(0, C.byref(st1))
+    assert st1.backing_allocs == st0.backing_allocs, "steady state must not reach cudaMalloc"
+    assert st1.reuse_hits >= st0.reuse_hits + 60
+    assert again.tobytes() == first.tobytes()
+    c, _ = dev.matmul(A, R.BFLOAT16, B, R.BFLOAT16)
+    assert c.tobytes() == first.tobytes()
+    # pinned staging gives the same answer
+    pa, pb, pc = C.c_void_p(), C.c_void_p(), C.c_void_p()
+    for p, arr in ((pa, A), (pb, B)):
+        tv._lib.check(lib.tvb_host_alloc(arr.nbytes, C.byref(p)))
+        C.memmove(p.value, arr.ctypes.data, arr.nbytes)
+    tv._lib.check(lib.tvb_host_alloc(first.nbytes, C.byref(pc)))
+    tv._lib.check(lib.tvb_matmul_host(0, pa, pb, pc, R.BFLOAT16, R.BFLOAT16, R.BFLOAT16, 1, 500, 256, 384))
+    pinned = np.frombuffer((C.c_char * first.nbytes).from_address(pc.value), dtype=np.uint16).reshape(first.shape)
+    assert pinned.tobytes() == first.tobytes()
+    for p in (pa, pb, pc):
+        tv._lib.check(lib.tvb_host_free(p))
+    # fp32 takes scratch from the pool too and releases nothing it still needs
+    A = R.fill((300, 512), R.FLOAT32, 3); B = R.fill((512, 260), R.FLOAT32, 4)
+    c32 = tv.ops.matmul_host(A, B, R.FLOAT32, R.FLOAT32)
+    exp, _ = R.oracle_matmul(A, R.FLOAT32, B, R.FLOAT32, "cuda")
+    assert R.rel_frobenius(c32, exp, R.FLOAT32) <= 1e-5
+
+
+@pytest.mark.parametrize("dt", range(8))
+def test_device_generator_is_bit_identical_to_host(dev, dt):
+    for dist in (0, 1):
+        p = dev.fill((5000,), dt, 0x5EED0004, dist, first=123)
+        got = dev.download(p, (5000,), dt)
+        assert got.tobytes() == R.fill((5000,), dt, 0x5EED0004, dist, first=123).tobytes()
+        dev.free(p)
+
+
+def test_fp32_split_is_exact_and_tf32_clean(dev, tv):
+    lib = tv._lib.lib
+    x = R.fill((4099,), R.FLOAT32, 5)[:4096].copy()
+    px = dev.upload(x); ph = dev.alloc(x.nbytes); pl = dev.alloc(x.nbytes)
+    tv._lib.check(lib.tvb_split_tf32(0, px, ph, pl, x.size, None))
+    hi = dev.download(ph, x.shape, R.FLOAT32); lo = dev.download(pl, x.shape, R.FLOAT32)
+    assert ((hi.view(np.uint32) & 0x1FFF) == 0).all() and ((lo.view(np.uint32) & 0x1FFF) == 0).all()
+    assert np.abs(x.astype(np.float64) - hi - lo).max() <= 2.0 ** -21 * np.abs(x).max()
+    for p in (px, ph, pl):
+        dev.free(p)
+
+
+def test_one_pass_tf32_mode_is_available_but_not_default(dev, tv):
+    lib = tv._lib.lib
+    A = R.fill((256, 1024), R.FLOAT32, 1); B = R.fill((1024, 256), R.FLOAT32, 2)
+    exp, _ = R.oracle_matmul(A, R.FLOAT32, B, R.FLOAT32, "cuda")
+    c3, _ = dev.matmul(A, R.FLOAT32, B, R.FLOAT32, algo=TCGEN05)
+    try:
+        assert lib.tvb_set_fp32_mode(1) == 0
+        c1, _ = dev.matmul(A, R.FLOAT32, B, R.FLOAT32, algo=TCGEN05)
+    finally:
+        assert lib.tvb_set_fp32_mode(0) == 0
+    e3, e1 = R.rel_frobenius(c3, exp, R.FLOAT32), R.rel_frobenius(c1, exp, R.FLOAT32)
+    assert e3 <= 1e-5 < e1 < 2e-3
+
+
+def test_bounded_wait_reports_and_context_survives(dev, tv):
+    """A wait that can never be satisfied runs out after its limit; the call returns
+    TVB_ERR_KERNEL_TIMEOUT, nothing hangs or faults, and the next matmul is correct."""
+    lib = tv._lib.lib
+    assert lib.tvb_selftest_wait_timeout(0, 50) == 7
+    assert b"wait ran out" in lib.tvb_last_error_string()
+    assert lib.tvb_sync(0) == 0  # the status word was cleared
+    A = R.fill((128, 64), R.BFLOAT16, 1); B = R.fill((64, 256), R.BFLOAT16, 2)
+    c, dtc = dev.matmul(A, R.BFLOAT16, B, R.BFLOAT16, algo=TCGEN05)
+    exp, dte = R.oracle_matmul(A, R.BFLOAT16, B, R.BFLOAT16, "cuda")
+    assert_matches(c, dtc, exp, dte)
+
+
+def test_sharded_decomposition_on_one_device(dev, tv):
+    """All ranks' shards computed one after another on one GPU: their union is the full product."""
+    from tensorvia_b200 import sharded
+    for dt, sa, sb in ((R.FLOAT32, (1000, 256), (256, 512)), (R.FLOAT16, (6, 200, 64), (6, 64, 128))):
+        A = R.fill(sa, dt, 1); B = R.fill(sb, dt, 2)
+        full, dtc = dev.matmul(A, dt, B, dt)
+        world = 4
+        parts = []
+        for r in range(world):
+            sh = sharded.plan(sa, sb, world, r)
+            if sh.count == 0:
+                continue
+            a_loc = A[sh.begin: sh.begin + sh.count]
+            b_loc = B if sh.axis == "rows" else B[sh.begin: sh.begin + sh.count]
+            parts.append(dev.matmul(a_loc, dt, b_loc, dt)[0])
+        assert np.concatenate(parts, axis=0).tobytes() == full.tobytes()
+
+
+def test_torch_facing_operator(tv):
+    import torch
+    a = torch.randn(300, 256, device="cuda").to(torch.bfloat16)
+    b = torch.randn(256, 512, device="cuda").to(torch.bfloat16)
+    c = tv.matmul(a, b)
+    torch.cuda.synchronize()
+    want = (a.double() @ b.double())
+    assert c.dtype == torch.bfloat16
+    assert (torch.linalg.norm(c.double() - want) / torch.linalg.norm(want)).item() < 1e-2
+    with pytest.raises(RuntimeError, match="contiguous"):
+        tv.matmul(a, b.t().contiguous().t())
+    with pytest.raises(RuntimeError, match="same rank"):
+        tv.matmul(a, b[None])
+    # int8 x fp16 promotes to fp32, as via::compute_type says
+    ai = torch.randint(-10, 11, (64, 32), device="cuda", dtype=torch.int8)
+    bh = torch.randn(32, 48, device="cuda").half()
+    ch = tv.matmul(ai, bh)
+    torch.cuda.synchronize()
+    assert ch.dtype == torch.float32
+    assert torch.allclose(ch, ai.float() @ bh.float(), rtol=1e-4, atol=1e-4)

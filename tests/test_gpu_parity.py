@@ -1,0 +1,173 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the oracle and the golden
+fixtures (outputs of the reference library).  Tolerances: integer results bit-exact; fp32
+results within 1e-5 relative Frobenius error; fp16/bf16 results (fp32 accumulation) within
+1e-2; fp64 within 1e-12."""
+import ctypes as C
+import json
+
+import numpy as np
+import pytest
+
+import refcheck as R
+from gpuutil import Dev, assert_matches
+
+pytestmark = pytest.mark.gpu
+
+META = json.loads((R.GOLDEN_DIR / "golden_meta.json").read_text())
+SMALL = np.load(R.GOLDEN_DIR / "golden_small.npz")
+TILED = np.load(R.GOLDEN_DIR / "golden_tiled.npz")
+F = lambda dt: 0 if dt >= R.BFLOAT16 else 1
+AUTO, TCGEN05, SIMT = 0, 1, 2
+TC_DTYPES = [R.BFLOAT16, R.FLOAT16, R.INT8, R.FLOAT32]
+
+
+@pytest.fixture(scope="module")
+def dev(tv):
+    d = Dev(tv)
+    yield d
+    d.free_all()
+
+
+# ---- every dtype pair ------------------------------------------------------------------------
+@pytest.mark.parametrize("a", range(8))
+@pytest.mark.parametrize("b", range(8))
+def test_all_dtype_pairs_against_golden_and_oracle(dev, a, b):
+    # INT64 with a float of 32 bits or fewer gives a FLOAT64 result from a FLOAT accumulator
+    # (decltype(int64 + float) is float, mul.cu:19): fp32 tolerance applies to those pairs
+    t64 = 1e-12 if R.FLOAT64 in (a, b) else 1e-5
+    # the reference's own outputs (CPU backend; same-type halves rounded as the CUDA backend does)
+    A = R.fill((5, 7), a, 1000 + a, F(a)); B = R.fill((7, 6), b, 2000 + b, F(b))
+    c, dtc = dev.matmul(A, a, B, b)
+    exp, dte = R.cuda_expected_from_cpu(SMALL[f"m2_{a}_{b}"], int(SMALL[f"m2_{a}_{b}_dt"]), a, b)
+    assert_matches(c, dtc, exp, dte, tol_f64=t64, what=f"golden 2-D {a}x{b}")
+    A3 = R.fill((2, 3, 4), a, 3000 + a, F(a)); B3 = R.fill((2, 4, 5), b, 4000 + b, F(b))
+    c, dtc = dev.matmul(A3, a, B3, b)
+    exp, dte = R.cuda_expected_from_cpu(SMALL[f"m3_{a}_{b}"], int(SMALL[f"m3_{a}_{b}_dt"]), a, b)
+    assert_matches(c, dtc, exp, dte, tol_f64=t64, what=f"golden 3-D {a}x{b}")
+    # a ragged shape that crosses tile edges of the CUDA-core kernel, against the oracle
+    A = R.fill((3, 70, 33), a, 11 + a, F(a)); B = R.fill((3, 33, 129), b, 22 + b, F(b))
+    c, dtc = dev.matmul(A, a, B, b)
+    exp, dte = R.oracle_matmul(A, a, B, b, "cuda")
+    assert_matches(c, dtc, exp, dte, tol_f64=t64, what=f"oracle ragged {a}x{b}")
+
+
+def test_float64_non_square_output(dev):
+    """The reference's CUDA launch passes rows for cols when the result is FLOAT64
+    (src/backend/cuda/mul.cu:91); the result here must be the true product."""
+    A = R.fill((40, 17), R.FLOAT64, 5); B = R.fill((17, 90), R.FLOAT64, 6)
+    c, dtc = dev.matmul(A, R.FLOAT64, B, R.FLOAT64)
+    assert dtc == R.FLOAT64 and np.allclose(c, A @ B, rtol=1e-13, atol=1e-13)
+
+
+# ---- tensor-core path: shape sweep -----------------------------------------------------------
+def _align(dt):
+    return {R.BFLOAT16: 8, R.FLOAT16: 8, R.INT8: 16, R.FLOAT32: 4}[dt]
+
+
+SWEEP = [(1, 1, 1), (1, 2, 1), (7, 1, 3), (127, 4, 9), (128, 8, 16), (129, 9, 17), (255, 16, 31),
+         (256, 3, 32), (257, 33, 33), (300, 5, 47), (64, 64, 1), (513, 2, 40)]
+
+
+@pytest.mark.parametrize("dt", TC_DTYPES)
+def test_tcgen05_shape_sweep(dev, dt):
+    """M free; K and N in units of 16 bytes (the TMA pitch rule) around the tile edges
+    (BLOCK_M 128, BLOCK_N 128/256, 128 bytes of K per stage, 4 or 6 stages)."""
+    al = _align(dt)
+    for i, (M, ku, nu) in enumerate(SWEEP):
+        K, N = ku * al, nu * al
+        A = R.fill((M, K), dt, 100 + i, F(dt)); B = R.fill((K, N), dt, 200 + i, F(dt))
+        c, dtc = dev.matmul(A, dt, B, dt, algo=TCGEN05)
+        exp, dte = R.oracle_matmul(A, dt, B, dt, "cuda")
+        assert_matches(c, dtc, exp, dte, what=f"dtype {dt} M={M} K={K} N={N}")
+
+
+@pytest.mark.parametrize("dt", TC_DTYPES)
+def test_tcgen05_batched_and_multi_tile(dev, dt):
+    al = _align(dt)
+    for i, (batch, M, K, N) in enumerate([(3, 130, 10 * al, 17 * al), (1, 700, 1056, 528), (5, 128, 256, 256),
+                                          (2, 260, 64, 784), (33, 9, 4 * al, 2 * al)]):
+        A = R.fill((batch, M, K), dt, 300 + i, F(dt)); B = R.fill((batch, K, N), dt, 400 + i, F(dt))
+        c, dtc = dev.matmul(A, dt, B, dt, algo=TCGEN05)
+        exp, dte = R.oracle_matmul(A, dt, B, dt, "cuda")
+        assert_matches(c, dtc, exp, dte, what=f"dtype {dt} batch={batch} M={M} K={K} N={N}")
+        # the same problem twice must give the same bits (pipeline phases, TMEM buffers)
+        c2, _ = dev.matmul(A, dt, B, dt, algo=TCGEN05)
+        assert c.tobytes() == c2.tobytes()
+
+
+@pytest.mark.parametrize("dt", TC_DTYPES)
+def test_tcgen05_and_simt_agree(dev, dt):
+    al = _align(dt)
+    A = R.fill((333, 24 * al), dt, 9, F(dt)); B = R.fill((24 * al, 20 * al), dt, 10, F(dt))
+    c1, d1 = dev.matmul(A, dt, B, dt, algo=TCGEN05)
+    c2, d2 = dev.matmul(A, dt, B, dt, algo=SIMT)
+    if dt == R.INT8:
+        assert d1 == d2 and c1.tobytes() == c2.tobytes()
+    else:
+        assert_matches(c1, d1, c2, d2, what="tcgen05 vs simt")
+
+
+def test_auto_falls_back_when_pitch_is_not_16_bytes(dev, tv):
+    # K = 30 halves = 60 bytes per row: TMA cannot address it; AUTO uses the CUDA-core kernel
+    A = R.fill((50, 30), R.BFLOAT16, 1); B = R.fill((30, 44), R.BFLOAT16, 2)
+    info = tv.ops.plan(R.BFLOAT16, R.BFLOAT16, 1, 50, 30, 44)
+    assert info.algo == SIMT
+    c, dtc = dev.matmul(A, R.BFLOAT16, B, R.BFLOAT16, algo=AUTO)
+    exp, dte = R.oracle_matmul(A, R.BFLOAT16, B, R.BFLOAT16, "cuda")
+    assert_matches(c, dtc, exp, dte)
+    with pytest.raises(tv._lib.TvbError) as e:
+        dev.matmul(A, R.BFLOAT16, B, R.BFLOAT16, algo=TCGEN05)
+    assert e.value.code == 9
+    info = tv.ops.plan(R.BFLOAT16, R.BFLOAT16, 1, 4096, 4096, 4096)
+    assert (info.algo, info.tile_m, info.tile_n, info.tile_k, info.passes) == (TCGEN05, 128, 256, 64, 1)
+    info = tv.ops.plan(R.FLOAT32, R.FLOAT32, 1, 2592, 2048, 4096)
+    assert info.algo == TCGEN05 and info.passes == 3 and info.workspace_bytes > 0
+
+
+# ---- the large-output path of the reference (mul_kernel_tiled) ----------------------------------
+@pytest.mark.parametrize("name", sorted(META["tiled"]))
+def test_against_reference_tiled_outputs(dev, name):
+    m = META["tiled"][name]
+    a, b = m["dta"], m["dtb"]
+    A = R.fill(tuple(m["shape_a"]), a, 5000 + a, F(a)); B = R.fill(tuple(m["shape_b"]), b, 6000 + b, F(b))
+    c, dtc = dev.matmul(A, a, B, b)
+    if name == "i8_f32":
+        # int8 x fp32 on a large output: the reference's CPU tiled kernel accumulates in A's type
+        # (int8, src/backend/cpu/mul.cpp:64) and is lossy; its CUDA kernel promotes to float
+        # (mul.cu:19).  The CUDA semantics are the contract.
+        exp, dte = R.oracle_matmul(A, a, B, b, "cuda")
+        assert_matches(c, dtc, exp, dte, what=name)
+        return
+    gold = TILED[f"{name}_rows"]
+    exp, dte = R.cuda_expected_from_cpu(gold, m["dtc"], a, b)
+    flat = c.reshape(-1, c.shape[-1])
+    assert_matches(flat[m["rows"]], dtc, exp, dte, what=name)
+    if dtc <= R.INT64:
+        assert R.sha(c) == m["sha_c"], "integer result differs from the reference somewhere"
+
+
+# ---- int8 wrap-around ------------------------------------------------------------------------------
+def test_int8_extremes_wrap_like_the_reference(dev):
+    """Sums far outside int8 keep their low byte (static_cast<int8_t>(int), mul.cu:46)."""
+    rng = np.random.default_rng(0)
+    A = rng.integers(-128, 128, (130, 512), dtype=np.int8); B = rng.integers(-128, 128, (512, 48), dtype=np.int8)
+    A[0, :] = -128; B[:, 0] = -128; A[1, :] = 127; B[:, 1] = 127
+    want = (A.astype(np.int64) @ B.astype(np.int64)).astype(np.int8)  # astype keeps the low byte
+    for algo in (TCGEN05, SIMT):
+        c, dtc = dev.matmul(A, R.INT8, B, R.INT8, algo=algo)
+        assert dtc == R.INT8 and (c == want).all()
+    exp, _ = R.oracle_matmul(A, R.INT8, B, R.INT8, "cuda")
+    assert (exp == want).all()
+
+
+def test_int8_accumulator_beyond_int32(dev):
+    """K = 131072 + 32 with every product (-128)*(-128): the exact sum passes 2^31.  The int
+    accumulator of the reference wraps; the low byte of the wrapped sum is what comes out."""
+    K = 131072 + 32
+    A = np.full((128, K), -128, dtype=np.int8); B = np.full((K, 16), -128, dtype=np.int8)
+    B[:, 1] = 127; B[:, 2] = 1; B[::2, 3] = 77
+    want = (A.astype(np.int64) @ B.astype(np.int64)).astype(np.int8)
+    c_simt, _ = dev.matmul(A, R.INT8, B, R.INT8, algo=SIMT)
+    assert (c_simt == want).all()
+    c_tc, _ = dev.matmul(A, R.INT8, B, R.INT8, algo=TCGEN05)
+    assert (c_tc == want).all(), "tensor-core s32 accumulator does not wrap modulo 2^32"
