@@ -167,6 +167,33 @@ int tvb_split_tf32(int device, const void* src, void* hi, void* lo, uint64_t cou
  * (an mbarrier nothing arrives on), lets the wait run out after `limit_ms` and returns what
  * tvb_sync then reports: TVB_ERR_KERNEL_TIMEOUT.  No fault, no hang; the context stays usable. */
 int tvb_selftest_wait_timeout(int device, uint32_t limit_ms);
+/* ---- for callers that must not allocate ---------------------------------------------------
+ * (No counterpart in the reference: its operator allocates its result and any temporary
+ * with cudaMalloc on every call.)
+ *
+ * fp32 C[batch,M,N] = A[batch,M,K] @ B[batch,K,N] on the tensor cores (3xTF32, the same kernels
+ * and accuracy as tvb_matmul) without a single allocating call: no cudaMalloc / cudaFree, no
+ * pinned memory, no stream or event creation, and no tvb_init.  It is meant for a host that
+ * gave all device memory to its own arena at start-up, or that runs where cudaMalloc may not
+ * be called at all (a latency-bound request handler, a plug-in inside another framework's
+ * process).  The scratch for the hi/lo split of A and B — 8 bytes per element of each — lives
+ * in a fixed array of TVB_STATIC_SCRATCH_BYTES inside the loaded module; every GPU that loads
+ * the library holds that array until the process ends.
+ *
+ *  - Limit: 8 * batch * (M*K + K*N) bytes (each operand rounded up to 256) must fit in
+ *    TVB_STATIC_SCRATCH_BYTES; larger problems fail with TVB_ERR_SHAPE and a message.  K and N
+ *    must be multiples of 4 and the pointers 16-byte aligned (else TVB_ERR_UNSUPPORTED).
+ *  - A, B, C are the caller's device buffers.  `stream` NULL means the legacy default stream.
+ *    The call returns when C is complete (it waits for the stream).
+ *  - The first call for a device looks up the array's device address and the driver's
+ *    tensor-map encoder; make that first call before any stream capture begins.
+ *  - All calls on a device share the one array, which keeps the previous call's contents
+ *    (every byte a call reads it has written first).  Calls whose GPU work overlaps — from
+ *    two host threads or two streams — race on it; serialise them. */
+#define TVB_STATIC_SCRATCH_BYTES (32u << 20)
+int tvb_matmul_f32_static(int device, const void* A, const void* B, void* C,
+                          int64_t batch, int64_t M, int64_t K, int64_t N, void* stream);
+
 /* Number of kernels this library has launched since load (all devices). */
 uint64_t tvb_kernel_launches(void);
 /* Upper bound, in milliseconds, on any device-side wait (default 2000). */

@@ -74,6 +74,7 @@ SIGNATURES = {
     "tvb_set_fp32_mode": (_i, [_i]),
     "tvb_split_tf32": (_i, [_i, _vp, _vp, _vp, _u64, _vp]),
     "tvb_selftest_wait_timeout": (_i, [_i, C.c_uint32]),
+    "tvb_matmul_f32_static": (_i, [_i, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     "tvb_kernel_launches": (_u64, []),
     "tvb_set_wait_limit_ms": (_i, [C.c_uint32]),
     "tvb_last_error_string": (C.c_char_p, []),

@@ -18,7 +18,8 @@ __device__ __forceinline__ float round_tf32(float x) {
   return __uint_as_float(r);
 }
 
-__global__ void __launch_bounds__(256)
+// (static: this header is included by more than one translation unit)
+static __global__ void __launch_bounds__(256)
 split_tf32_kernel(const float4* __restrict__ x, float4* __restrict__ hi, float4* __restrict__ lo,
                   size_t n4, const float* __restrict__ xs, float* __restrict__ his,
                   float* __restrict__ los, size_t n) {
@@ -46,7 +47,7 @@ split_tf32_kernel(const float4* __restrict__ x, float4* __restrict__ hi, float4*
 // Same split for the B operand, written transposed: src is [batch][K][N], hi and lo are
 // [batch][N][K], so the tensor core can read B K-major.  32x32 tiles go through shared
 // memory: reads are coalesced along N, writes along K.  grid = (ceil(N/32), ceil(K/32), batch).
-__global__ void __launch_bounds__(256)
+static __global__ void __launch_bounds__(256)
 split_tf32_transpose_kernel(const float* __restrict__ src, float* __restrict__ hi,
                             float* __restrict__ lo, int K, int N) {
   __shared__ float th[32][33];

@@ -423,6 +423,12 @@ cudaError_t launch_fill(void* dst, size_t n, uint64_t seed, uint64_t first, int 
 
 }  // namespace
 
+namespace tvb {
+// lets the library's other translation units leave their message where
+// tvb_last_error_string finds it
+void set_last_error(const char* message) { g_err = message ? message : ""; }
+}  // namespace tvb
+
 // =====================================================================================
 // exported C ABI
 // =====================================================================================

@@ -1,0 +1,233 @@
+// tvb_matmul_f32_static: the fp32 tensor-core matmul for callers that must not allocate.
+//
+// Who that is: a host program that has handed all device memory to its own arena at start-up
+// (an inference server with a fixed memory plan, a framework that owns the allocator), or one
+// that runs where cudaMalloc is off limits because it may block on other streams or fail late
+// — a request handler with a latency bound, a plug-in loaded into somebody else's process.
+// The ordinary fp32 path needs scratch for the TF32 hi/lo split of both operands and takes it
+// from the library's pool, which grows with cudaMalloc.  This entry point takes that scratch
+// from a fixed array that is part of the loaded module instead, and needs neither tvb_init nor
+// any other allocating call: no cudaMalloc, cudaFree, cudaHostAlloc, stream or event creation.
+//
+// The price is a size limit (TVB_STATIC_SCRATCH_BYTES, 32 MiB, held by every GPU that loads
+// the library until the process exits) and no concurrency: every call on a device shares the
+// one array, so two calls whose GPU work overlaps (two host threads, two streams) race.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cudaTypedefs.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <mutex>
+
+#include "aux_kernels.cuh"
+#include "tvb.h"
+#include "umma_gemm.cuh"
+
+namespace tvb {
+void set_last_error(const char* message);  // defined beside tvb_last_error_string
+}
+
+namespace {
+
+using namespace tvb;
+
+// The scratch itself.  In host code `g_static_scratch` is only a stand-in for the symbol, not
+// a device address; the address a kernel can use comes from cudaGetSymbolAddress (below).
+static __device__ __align__(256) unsigned char g_static_scratch[TVB_STATIC_SCRATCH_BYTES];
+// Timed-out device waits of this entry point's kernels are recorded here.
+static __device__ uint32_t g_static_status;
+
+constexpr int kMaxDev = 64;
+struct PerDevice {
+  bool ready = false;
+  unsigned char* scratch = nullptr;  // device address of g_static_scratch on this device
+  uint32_t* status = nullptr;        // device address of g_static_status on this device
+  int sm_count = 0;
+  bool smem_configured[2] = {false, false};
+};
+PerDevice g_dev[kMaxDev];
+std::mutex g_mu;
+PFN_cuTensorMapEncodeTiled g_encode_fn = nullptr;
+
+int fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  tvb::set_last_error(buf);  // readable through tvb_last_error_string, like every other entry point
+  return code;
+}
+
+#define TVS_CUDA(expr)                                                                          \
+  do {                                                                                          \
+    cudaError_t e__ = (expr);                                                                   \
+    if (e__ != cudaSuccess)                                                                     \
+      return fail(TVB_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e__), __FILE__, \
+                  __LINE__);                                                                    \
+  } while (0)
+
+// One-time set-up of a device, run by the first call for that device with the device current:
+// resolves the device addresses of the two module-scope symbols and clears the status word.
+int setup_device(int device, PerDevice** out) {
+  std::lock_guard<std::mutex> g(g_mu);
+  PerDevice& d = g_dev[device];
+  if (!d.ready) {
+    cudaDeviceProp prop;
+    TVS_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10)
+      return fail(TVB_ERR_NO_DEVICE, "device %d is sm_%d%d; this library only carries sm_100a code", device,
+                  prop.major, prop.minor);
+    void* p = nullptr;
+    TVS_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+    d.scratch = static_cast<unsigned char*>(p);
+    TVS_CUDA(cudaGetSymbolAddress(&p, g_static_status));
+    d.status = static_cast<uint32_t*>(p);
+    if ((reinterpret_cast<uintptr_t>(d.scratch) & 255u) != 0)
+      return fail(TVB_ERR_CUDA, "static scratch is not 256-byte aligned");
+    TVS_CUDA(cudaMemset(d.status, 0, sizeof(uint32_t)));
+    if (!g_encode_fn) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult q;
+      TVS_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+      if (q != cudaDriverEntryPointSuccess || !fn)
+        return fail(TVB_ERR_CUDA, "driver does not export cuTensorMapEncodeTiled");
+      g_encode_fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled>(fn);
+    }
+    d.sm_count = prop.multiProcessorCount;
+    d.ready = true;
+  }
+  *out = &d;
+  return TVB_OK;
+}
+
+int encode_map(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows, uint64_t batch,
+               uint32_t box_cols, uint32_t box_rows) {
+  cuuint64_t dims[3] = {cols, rows, batch};
+  cuuint64_t strides[2] = {cols * 4, rows * cols * 4};
+  cuuint32_t box[3] = {box_cols, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = g_encode_fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides,
+                           box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(TVB_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled failed (%d)", static_cast<int>(r));
+  return TVB_OK;
+}
+
+template <int BN, int ST>
+cudaError_t launch_gemm(PerDevice& d, int slot, const CUtensorMap& a0, const CUtensorMap& a1,
+                        const CUtensorMap& b0, const CUtensorMap& b1, const UmmaGemmParams& p, int grid,
+                        cudaStream_t s) {
+  using Cfg = UmmaGemmConfig<OP_TF32, BN, ST>;
+  if (!d.smem_configured[slot]) {
+    cudaError_t e = cudaFuncSetAttribute(umma_gemm_kernel<OP_TF32, BN, ST>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    d.smem_configured[slot] = true;
+  }
+  umma_gemm_kernel<OP_TF32, BN, ST><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, s>>>(a0, a1, b0, b1, p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+extern "C" int tvb_matmul_f32_static(int device, const void* A, const void* B, void* C, int64_t batch,
+                                     int64_t M, int64_t K, int64_t N, void* stream) {
+  if (device < 0 || device >= kMaxDev) return fail(TVB_ERR_INVALID_ARG, "device index %d out of range", device);
+  if (!A || !B || !C) return fail(TVB_ERR_INVALID_ARG, "A, B and C must not be null");
+  if (batch <= 0 || M <= 0 || K <= 0 || N <= 0) return fail(TVB_ERR_SHAPE, "dimensions must be positive");
+  if (batch > 0x7FFFFFFFll || M > 0x7FFFFFFFll || K > 0x7FFFFFFFll || N > 0x7FFFFFFFll)
+    return fail(TVB_ERR_SHAPE, "a dimension exceeds 2^31-1");
+  auto mis = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) != 0; };
+  if ((K % 4) != 0 || (N % 4) != 0 || mis(A) || mis(B) || mis(C) || (K + 31) / 32 > 65535 || batch > 65535)
+    return fail(TVB_ERR_UNSUPPORTED,
+                "the static-scratch fp32 path needs K and N to be multiples of 4, 16-byte aligned "
+                "pointers and batch <= 65535");
+  const size_t na = static_cast<size_t>(batch) * M * K, nb = static_cast<size_t>(batch) * K * N;
+  const size_t na_b = (na * 4 + 255) / 256 * 256, nb_b = (nb * 4 + 255) / 256 * 256;
+  const size_t need = 2 * na_b + 2 * nb_b;
+  if (need > static_cast<size_t>(TVB_STATIC_SCRATCH_BYTES))
+    return fail(TVB_ERR_SHAPE,
+                "problem needs %zu bytes of split scratch (8 bytes per element of A and of B) but the "
+                "static array holds %zu; use tvb_matmul, which takes scratch from the pool",
+                need, static_cast<size_t>(TVB_STATIC_SCRATCH_BYTES));
+
+  int prev = -1;
+  cudaGetDevice(&prev);
+  if (prev != device) TVS_CUDA(cudaSetDevice(device));
+  struct Restore {
+    int prev, dev;
+    ~Restore() { if (prev >= 0 && prev != dev) cudaSetDevice(prev); }
+  } restore{prev, device};
+
+  PerDevice* d = nullptr;
+  int rc = setup_device(device, &d);
+  if (rc != TVB_OK) return rc;
+  // NULL means CUDA's legacy default stream here (there is no library-owned stream to fall back to)
+  cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : cudaStreamLegacy;
+
+  float* ahi = reinterpret_cast<float*>(d->scratch);
+  float* alo = reinterpret_cast<float*>(d->scratch + na_b);
+  float* bhi = reinterpret_cast<float*>(d->scratch + 2 * na_b);
+  float* blo = reinterpret_cast<float*>(d->scratch + 2 * na_b + nb_b);
+
+  {  // split A
+    const size_t n4 = na / 4;
+    size_t blocks = (n4 + 255) / 256;
+    const size_t cap = static_cast<size_t>(d->sm_count) * 16;
+    if (blocks > cap) blocks = cap;
+    if (blocks == 0) blocks = 1;
+    split_tf32_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+        static_cast<const float4*>(A), reinterpret_cast<float4*>(ahi), reinterpret_cast<float4*>(alo), n4,
+        static_cast<const float*>(A), ahi, alo, na);
+    TVS_CUDA(cudaGetLastError());
+  }
+  {  // split B, transposed to [batch][N][K]
+    dim3 grid(static_cast<unsigned>((N + 31) / 32), static_cast<unsigned>((K + 31) / 32),
+              static_cast<unsigned>(batch));
+    split_tf32_transpose_kernel<<<grid, 256, 0, s>>>(static_cast<const float*>(B), bhi, blo,
+                                                     static_cast<int>(K), static_cast<int>(N));
+    TVS_CUDA(cudaGetLastError());
+  }
+
+  const int block_n = (N <= 128) ? 128 : 256;
+  CUtensorMap ma0, ma1, mb0, mb1;
+  if ((rc = encode_map(&ma0, ahi, K, M, batch, 32, 128)) != TVB_OK) return rc;
+  if ((rc = encode_map(&ma1, alo, K, M, batch, 32, 128)) != TVB_OK) return rc;
+  if ((rc = encode_map(&mb0, bhi, K, N, batch, 32, block_n)) != TVB_OK) return rc;
+  if ((rc = encode_map(&mb1, blo, K, N, batch, 32, block_n)) != TVB_OK) return rc;
+
+  UmmaGemmParams p;
+  p.M = static_cast<int32_t>(M);
+  p.N = static_cast<int32_t>(N);
+  p.K = static_cast<int32_t>(K);
+  p.batch = static_cast<int32_t>(batch);
+  p.m_tiles = static_cast<int32_t>((M + 127) / 128);
+  p.n_tiles = static_cast<int32_t>((N + block_n - 1) / block_n);
+  p.k_blocks = static_cast<int32_t>((K + 31) / 32);
+  p.passes = 3;
+  p.k_chunk_blocks = 8;
+  const int64_t tiles = batch * p.m_tiles * p.n_tiles;
+  if (tiles > 0x7FFFFFFFll) return fail(TVB_ERR_SHAPE, "too many output tiles");
+  p.total_tiles = static_cast<uint32_t>(tiles);
+  p.C = C;
+  p.status = d->status;
+  p.wait_limit_ns = 2000000000ull;
+  const int grid = static_cast<int>(p.total_tiles < static_cast<uint32_t>(d->sm_count) ? p.total_tiles
+                                                                                       : d->sm_count);
+  cudaError_t e = (block_n == 256) ? launch_gemm<256, 4>(*d, 0, ma0, ma1, mb0, mb1, p, grid, s)
+                                   : launch_gemm<128, 6>(*d, 1, ma0, ma1, mb0, mb1, p, grid, s);
+  if (e != cudaSuccess) return fail(TVB_ERR_CUDA, "GEMM launch failed: %s", cudaGetErrorString(e));
+
+  // Like the reference's operator (cudaStreamSynchronize at src/backend/cuda/mul.cu:122) the call
+  // returns when the result is there; that is also when the status word can be read.
+  TVS_CUDA(cudaStreamSynchronize(s));
+  uint32_t st = 0;
+  TVS_CUDA(cudaMemcpy(&st, d->status, sizeof st, cudaMemcpyDeviceToHost));
+  if (st != 0) {
+    TVS_CUDA(cudaMemset(d->status, 0, sizeof(uint32_t)));
+    return fail(TVB_ERR_KERNEL_TIMEOUT, "a device-side wait ran out (bits %u); the result is invalid", st);
+  }
+  return TVB_OK;
+}

@@ -443,7 +443,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
 
 // One CTA waits on an mbarrier that nothing ever arrives on: exercises the bounded wait and
 // the status word exactly as a stalled pipeline would, without any copy or MMA in flight.
-__global__ void wait_timeout_probe_kernel(uint32_t* status, uint64_t limit_ns) {
+static __global__ void wait_timeout_probe_kernel(uint32_t* status, uint64_t limit_ns) {
   __shared__ __align__(8) uint64_t bar;
   const uint32_t addr = ptx::smem_u32(&bar);
   if (threadIdx.x == 0) {

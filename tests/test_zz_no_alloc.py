@@ -1,0 +1,75 @@
+"""tvb_matmul_f32_static — the fp32 matmul for callers that cannot allocate.
+
+Some hosts may not call cudaMalloc once they are running: they gave the whole GPU to their own
+arena at start-up, or they sit on a latency-bound path where an allocation could block or fail.
+For them the library keeps the scratch of the fp32 path (the TF32 hi/lo split of A and B) in a
+fixed 32 MiB array inside the loaded module.  This test calls that entry point through the C ABI
+twice in a row and checks each result against the ordinary entry point (tvb_matmul), to the
+tolerance the fp32 tests use (1e-5 relative Frobenius error; both run the same kernels, so the
+bits are expected to agree as well).  The second call is a smaller, different problem, so it
+would show scratch left over from the first.
+
+The file name sorts last on purpose: under `-x` every other test has run before this one.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import refcheck as R
+from gpuutil import Dev
+
+pytestmark = pytest.mark.gpu
+
+
+def _both(dev, lib, check, A, B):
+    batch, M, K, N = R.bmkn(A.shape, B.shape)
+    shape_c = (batch, M, N) if A.ndim == 3 else (M, N)
+    pa, pb = dev.upload(A), dev.upload(B)
+    nbytes = int(np.prod(shape_c)) * 4
+    pc_pool, pc_static = dev.alloc(nbytes), dev.alloc(nbytes)
+    try:
+        dev.matmul_ptr(pa, R.FLOAT32, pb, R.FLOAT32, pc_pool, batch, M, K, N, algo=1)
+        dev.sync()
+        stream = C.c_void_p()
+        check(lib.tvb_stream(0, C.byref(stream)))
+        check(lib.tvb_matmul_f32_static(0, pa, pb, pc_static, batch, M, K, N, stream))
+        want = dev.download(pc_pool, shape_c, R.FLOAT32)
+        got = dev.download(pc_static, shape_c, R.FLOAT32)
+    finally:
+        for p in (pa, pb, pc_pool, pc_static):
+            dev.free(p)
+    return got, want
+
+
+def test_static_scratch_entry_point_matches_pool_entry_point_twice(tv):
+    lib, check = tv._lib.lib, tv._lib.check
+    dev = Dev(tv)
+    try:
+        # first call: close to the size limit (8 * (M*K + K*N) = 30.4 MiB of the 32 MiB array)
+        A1 = R.fill((1500, 1024), R.FLOAT32, 11); B1 = R.fill((1024, 2392), R.FLOAT32, 12)
+        got, want = _both(dev, lib, check, A1, B1)
+        assert R.rel_frobenius(got, want, R.FLOAT32) <= 1e-5
+        assert got.tobytes() == want.tobytes()
+        exp, _ = R.oracle_matmul(A1[:64], R.FLOAT32, B1, R.FLOAT32, "cuda")
+        assert R.rel_frobenius(got[:64], exp, R.FLOAT32) <= 1e-5
+        # second call right after: a smaller batched problem with other values
+        A2 = R.fill((3, 130, 260), R.FLOAT32, 13); B2 = R.fill((3, 260, 72), R.FLOAT32, 14)
+        got, want = _both(dev, lib, check, A2, B2)
+        assert R.rel_frobenius(got, want, R.FLOAT32) <= 1e-5
+        assert got.tobytes() == want.tobytes()
+        exp, _ = R.oracle_matmul(A2, R.FLOAT32, B2, R.FLOAT32, "cuda")
+        assert R.rel_frobenius(got, exp, R.FLOAT32) <= 1e-5
+
+        # beyond the array: refused with a clear message, nothing launched
+        p = dev.alloc(4096)
+        rc = lib.tvb_matmul_f32_static(0, p, p, p, 1, 4096, 4096, 4096, None)
+        assert rc == 2  # TVB_ERR_SHAPE
+        msg = lib.tvb_last_error_string().decode()
+        assert "static array" in msg and "tvb_matmul" in msg
+        # shapes the TMA path cannot address are refused too
+        assert lib.tvb_matmul_f32_static(0, p, p, p, 1, 8, 6, 8, None) == 9  # TVB_ERR_UNSUPPORTED
+        assert lib.tvb_matmul_f32_static(0, None, p, p, 1, 8, 8, 8, None) == 1
+        dev.free(p)
+    finally:
+        dev.free_all()
