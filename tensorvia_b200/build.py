@@ -70,7 +70,8 @@ def build_host_cpp(force: bool = False) -> Path | None:
     srcs = sorted((CPP / "src").glob("*.cpp"))
     hdrs = sorted((CPP / "include").rglob("*.h"))
     cxx = shutil.which("g++") or "g++"
-    common = ["-std=gnu++20", "-O2", "-fPIC", f"-I{CPP / 'include'}", f"-I{CPP / 'include' / 'core'}",
+    cxx = "/usr/bin/g++" if Path("/usr/bin/g++").exists() else cxx
+    common = ["-std=gnu++20", "-O2", "-fPIC", "-Wall", f"-I{CPP / 'include'}", f"-I{CPP / 'include' / 'core'}",
               f"-I{ROOT / 'include'}"]
     if force or _stale(target, srcs + hdrs + [LIB / "libtvb.so"]):
         _run([cxx, *common, "-shared", *srcs, f"-L{LIB}", "-ltvb", "-Wl,-rpath,$ORIGIN", "-o", target])

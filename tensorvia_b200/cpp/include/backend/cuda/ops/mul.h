@@ -1,0 +1,14 @@
+// Backend operator slot of the matmul, shaped as the reference's
+// include/backend/cuda/ops/mul.h: ops::Mul dispatches to MulImpl<Device::CUDA>::execute.
+#pragma once
+#include "ops.h"
+
+namespace ops {
+template <via::Device D>
+struct MulImpl;
+
+template <>
+struct MulImpl<via::Device::CUDA> {
+  static Tensor execute(const Tensor& a, const Tensor& b);
+};
+}  // namespace ops

@@ -1,0 +1,68 @@
+// Concrete storage and context classes of the host layer (internal to the layer and its tests).
+#pragma once
+#include <memory>
+
+#include "context.h"
+#include "tensor.h"
+
+namespace tvhost {
+
+void check(int rc, const char* what);  // throws std::runtime_error with the C library's message
+
+// One per device index: the C library's stream for that device, and a blocking wait that also
+// surfaces a timed-out device-side wait as an exception.
+class CudaContext final : public ContextImpl {
+ public:
+  explicit CudaContext(int device);
+  void* ctx_raw_ptr() override { return &m_stream; }  // -> cudaStream_t*
+  void* stream() const { return m_stream; }
+  int device() const { return m_device; }
+  void wait();
+
+ private:
+  int m_device;
+  void* m_stream = nullptr;
+};
+std::shared_ptr<CudaContext> cuda_context(int device);
+
+class HostStorage final : public TensorImpl {
+ public:
+  HostStorage(void* src, size_t numel, via::DataType dtype);
+  ~HostStorage() override;
+  void* data() override { return m_data; }
+  const void* data() const override { return m_data; }
+  size_t numel() const override { return m_numel; }
+  size_t bytes() const { return m_numel * via::calc_dtype_size(m_dtype); }
+  void copy_to(std::shared_ptr<TensorImpl> dst) const override;
+  std::unique_ptr<TensorImpl> clone() const override;
+  std::unique_ptr<TensorImpl> clone_as_contiguous(const Metadata&) const override;
+  std::shared_ptr<ContextImpl> context() const override;
+
+ private:
+  void* m_data = nullptr;
+  size_t m_numel;
+  via::DataType m_dtype;
+};
+
+class CudaStorage final : public TensorImpl {
+ public:
+  CudaStorage(void* host_src, size_t numel, via::DataType dtype, std::shared_ptr<CudaContext> ctx);
+  ~CudaStorage() override;
+  void* data() override { return m_data; }
+  const void* data() const override { return m_data; }
+  size_t numel() const override { return m_numel; }
+  size_t bytes() const { return m_numel * via::calc_dtype_size(m_dtype); }
+  void copy_to(std::shared_ptr<TensorImpl> dst) const override;
+  std::unique_ptr<TensorImpl> clone() const override;
+  std::unique_ptr<TensorImpl> clone_as_contiguous(const Metadata&) const override;
+  std::shared_ptr<ContextImpl> context() const override;
+  const std::shared_ptr<CudaContext>& cuda() const { return m_ctx; }
+
+ private:
+  void* m_data = nullptr;
+  size_t m_numel;
+  via::DataType m_dtype;
+  std::shared_ptr<CudaContext> m_ctx;
+};
+
+}  // namespace tvhost

@@ -1,0 +1,36 @@
+// MulImpl<Device::CUDA>::execute over the C ABI (reference: src/backend/cuda/mul.cu:52-124).
+#include "backend/cuda/ops/mul.h"
+#include "factory.h"
+#include "storage.h"
+#include "tvb.h"
+
+using namespace via;
+
+namespace ops {
+
+Tensor MulImpl<Device::CUDA>::execute(const Tensor& a, const Tensor& b) {
+  const bool batched = a.dims() == 3;
+  const int64_t batch = batched ? a.shape(0) : 1;
+  const int64_t M = batched ? a.shape(1) : a.shape(0);
+  const int64_t K = batched ? a.shape(2) : a.shape(1);
+  const int64_t N = batched ? b.shape(2) : b.shape(1);
+  const DataType res_type = compute_type(a.dtype(), b.dtype());
+
+  auto sa = std::dynamic_pointer_cast<tvhost::CudaStorage>(a.get_impl());
+  auto sb = std::dynamic_pointer_cast<tvhost::CudaStorage>(b.get_impl());
+  if (!sa || !sb) throw std::runtime_error("MulImpl<CUDA>: operands must live on a CUDA device");
+  if (sa->cuda()->device() != sb->cuda()->device()) throw std::runtime_error("Tensors a and b device mismatch!");
+  const int dev = sa->cuda()->device();
+
+  // the result is created on the operands' device, from the pool
+  auto sc = std::make_shared<tvhost::CudaStorage>(nullptr, static_cast<size_t>(batch * M * N), res_type, sa->cuda());
+  tvhost::check(tvb_matmul(dev, a.data(), b.data(), sc->data(), static_cast<int>(a.dtype()), static_cast<int>(b.dtype()),
+                           static_cast<int>(res_type), batch, M, K, N, nullptr),
+                "tvb_matmul");
+  sa->cuda()->wait();  // every op of the reference returns with its result complete (mul.cu:122)
+
+  std::vector<int64_t> shape = batched ? std::vector<int64_t>{batch, M, N} : std::vector<int64_t>{M, N};
+  return tvhost::adopt(std::move(shape), res_type, sc, Device::CUDA);
+}
+
+}  // namespace ops

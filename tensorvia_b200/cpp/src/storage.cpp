@@ -1,0 +1,173 @@
+// Storage, contexts and the registry of the host layer.
+//
+// Replaces, for the matmul path, the reference's CUDATensor / CUDAContext / factory / static
+// registrar (include/backend/cuda/cuda_tensor.{h,cpp}, cuda_context.h, src/factory.cpp,
+// src/init.cpp:18-34): device blocks come from the C library's caching pool (tvb_malloc)
+// instead of one cudaMalloc per tensor, and a context exists per device index instead of one
+// global device.
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <stdexcept>
+#include <string>
+
+#include "context.h"
+#include "factory.h"
+#include "storage.h"
+#include "tvb.h"
+
+using namespace via;
+
+namespace tvhost {
+
+void check(int rc, const char* what) {
+  if (rc != TVB_OK) throw std::runtime_error(std::string(what) + ": " + tvb_last_error_string());
+}
+
+// ---- contexts ---------------------------------------------------------------------------
+class HostContext final : public ContextImpl {
+ public:
+  void* ctx_raw_ptr() override { return nullptr; }
+};
+
+std::shared_ptr<CudaContext> cuda_context(int device) {
+  static std::mutex mu;
+  static std::map<int, std::shared_ptr<CudaContext>> ctxs;
+  std::lock_guard<std::mutex> g(mu);
+  auto it = ctxs.find(device);
+  if (it != ctxs.end()) return it->second;
+  check(tvb_init(device), "tvb_init");
+  auto c = std::make_shared<CudaContext>(device);
+  ctxs[device] = c;
+  return c;
+}
+
+CudaContext::CudaContext(int device) : m_device(device) { check(tvb_stream(device, &m_stream), "tvb_stream"); }
+void CudaContext::wait() { check(tvb_sync(m_device), "tvb_sync"); }
+
+// ---- host storage ------------------------------------------------------------------------
+HostStorage::HostStorage(void* src, size_t numel, DataType dtype) : m_numel(numel), m_dtype(dtype) {
+  const size_t bytes = numel * calc_dtype_size(dtype);
+  m_data = std::malloc(bytes);
+  if (!m_data) throw std::runtime_error("host allocation failed");
+  if (src) std::memcpy(m_data, src, bytes);
+}
+HostStorage::~HostStorage() { std::free(m_data); }
+void HostStorage::copy_to(std::shared_ptr<TensorImpl> dst) const {
+  auto d = std::dynamic_pointer_cast<HostStorage>(dst);
+  if (!d || d->m_numel != m_numel || d->m_dtype != m_dtype) throw std::runtime_error("copy_to: incompatible destination");
+  std::memcpy(d->m_data, m_data, bytes());
+}
+std::unique_ptr<TensorImpl> HostStorage::clone() const {
+  return std::make_unique<HostStorage>(m_data, m_numel, m_dtype);
+}
+std::unique_ptr<TensorImpl> HostStorage::clone_as_contiguous(const Metadata&) const { return clone(); }
+std::shared_ptr<ContextImpl> HostStorage::context() const {
+  static auto ctx = std::make_shared<HostContext>();
+  return ctx;
+}
+
+// ---- device storage ----------------------------------------------------------------------
+CudaStorage::CudaStorage(void* host_src, size_t numel, DataType dtype, std::shared_ptr<CudaContext> ctx)
+    : m_numel(numel), m_dtype(dtype), m_ctx(std::move(ctx)) {
+  check(tvb_malloc(m_ctx->device(), bytes(), &m_data), "tvb_malloc");
+  if (host_src) {
+    check(tvb_memcpy_h2d(m_ctx->device(), m_data, host_src, bytes(), nullptr), "tvb_memcpy_h2d");
+    m_ctx->wait();  // the caller's buffer may go away right after the constructor returns
+  }
+}
+CudaStorage::~CudaStorage() {
+  // the stream may still be using the block: drain it before the block returns to the pool
+  tvb_sync(m_ctx->device());
+  tvb_free(m_ctx->device(), m_data);
+}
+void CudaStorage::copy_to(std::shared_ptr<TensorImpl> dst) const {
+  auto d = std::dynamic_pointer_cast<CudaStorage>(dst);
+  if (!d || d->m_numel != m_numel || d->m_dtype != m_dtype || d->m_ctx->device() != m_ctx->device())
+    throw std::runtime_error("copy_to: incompatible destination");
+  check(tvb_memcpy_d2d(m_ctx->device(), d->m_data, m_data, bytes(), nullptr), "tvb_memcpy_d2d");
+  m_ctx->wait();
+}
+std::unique_ptr<TensorImpl> CudaStorage::clone() const {
+  auto c = std::make_unique<CudaStorage>(nullptr, m_numel, m_dtype, m_ctx);
+  check(tvb_memcpy_d2d(m_ctx->device(), c->m_data, m_data, bytes(), nullptr), "tvb_memcpy_d2d");
+  m_ctx->wait();
+  return c;
+}
+std::unique_ptr<TensorImpl> CudaStorage::clone_as_contiguous(const Metadata&) const { return clone(); }
+std::shared_ptr<ContextImpl> CudaStorage::context() const { return m_ctx; }
+
+}  // namespace tvhost
+
+// ---- registry ------------------------------------------------------------------------------
+namespace {
+std::map<Device, TensorImplFactory>& factories() {
+  static std::map<Device, TensorImplFactory> f;
+  return f;
+}
+std::mutex g_reg_mu;
+int g_default_device = 0;
+
+// Registers the CUDA and CPU factories when the library is loaded (the reference does this
+// from a static CUDARegistrar, src/init.cpp:21-33).  No device is touched until the first
+// CUDA tensor is created.
+struct Registrar {
+  Registrar() {
+    register_tensor_impl(Device::CPU, [](void* p, size_t n, DataType t) {
+      return std::make_shared<tvhost::HostStorage>(p, n, t);
+    });
+    register_tensor_impl(Device::CUDA, [](void* p, size_t n, DataType t) {
+      return std::make_shared<tvhost::CudaStorage>(p, n, t, tvhost::cuda_context(default_device()));
+    });
+  }
+} g_registrar;
+}  // namespace
+
+void set_default_device(int device) {
+  if (device < 0) throw std::invalid_argument("device index must not be negative");
+  g_default_device = device;
+}
+int default_device() { return g_default_device; }
+
+void register_tensor_impl(Device device, TensorImplFactory factory) {
+  std::lock_guard<std::mutex> g(g_reg_mu);
+  factories()[device] = std::move(factory);
+}
+
+static std::shared_ptr<TensorImpl> make_impl(void* ptr, size_t numel, DataType dtype, Device device) {
+  if (numel == 0) throw std::invalid_argument("numel must be bigger than 0");
+  TensorImplFactory f;
+  {
+    std::lock_guard<std::mutex> g(g_reg_mu);
+    auto it = factories().find(device);
+    if (it == factories().end())
+      throw std::runtime_error("No tensor implementation registered for device: " + std::string(device_to_string(device)));
+    f = it->second;
+  }
+  return f(ptr, numel, dtype);
+}
+std::shared_ptr<TensorImpl> create_tensor_impl(size_t numel, DataType dtype, Device device) {
+  return make_impl(nullptr, numel, dtype, device);
+}
+std::shared_ptr<TensorImpl> create_tensor_impl(void* ptr, size_t numel, DataType dtype, Device device) {
+  if (!ptr) throw std::runtime_error("create_tensor_impl: ptr is null");
+  return make_impl(ptr, numel, dtype, device);
+}
+
+void copy_device_to_host(std::shared_ptr<TensorImpl> src, std::shared_ptr<TensorImpl> dst, DataType dtype) {
+  auto s = std::dynamic_pointer_cast<tvhost::CudaStorage>(src);
+  auto d = std::dynamic_pointer_cast<tvhost::HostStorage>(dst);
+  if (!s || !d || s->numel() != d->numel()) throw std::runtime_error("copy_device_to_host: bad operands");
+  const size_t bytes = s->numel() * calc_dtype_size(dtype);
+  tvhost::check(tvb_memcpy_d2h(s->cuda()->device(), d->data(), s->data(), bytes, nullptr), "tvb_memcpy_d2h");
+  s->cuda()->wait();
+}
+void copy_host_to_device(std::shared_ptr<TensorImpl> src, std::shared_ptr<TensorImpl> dst, DataType dtype) {
+  auto s = std::dynamic_pointer_cast<tvhost::HostStorage>(src);
+  auto d = std::dynamic_pointer_cast<tvhost::CudaStorage>(dst);
+  if (!s || !d || s->numel() != d->numel()) throw std::runtime_error("copy_host_to_device: bad operands");
+  const size_t bytes = s->numel() * calc_dtype_size(dtype);
+  tvhost::check(tvb_memcpy_h2d(d->cuda()->device(), d->data(), s->data(), bytes, nullptr), "tvb_memcpy_h2d");
+  d->cuda()->wait();
+}

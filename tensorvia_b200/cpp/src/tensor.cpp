@@ -1,0 +1,170 @@
+// Tensor: construction, value semantics, host/device moves, creation helpers.
+#include <cstring>
+#include <mutex>
+#include <random>
+
+#include "factory.h"
+#include "ops.h"
+#include "storage.h"
+#include "tvb.h"
+
+using namespace via;
+
+namespace {
+// The layer is a CUDA build: like the reference compiled with BACKEND_CUDA, tensors are created
+// on the device unless a host device is named (the reference ignores the argument,
+// src/tensor.cpp:96-117; honouring Device::CPU here is what makes host staging possible).
+constexpr Device kDefaultDevice = Device::CUDA;
+
+std::mt19937_64& rng() {
+  static std::mt19937_64 g(0x5EED5EEDull);
+  return g;
+}
+std::mutex g_rng_mu;
+
+// writes float `v` as one element of `dtype` at dst[i]; integers truncate toward zero
+void store_value(void* dst, size_t i, DataType dtype, double v) {
+  switch (dtype) {
+    case DataType::INT8: static_cast<int8_t*>(dst)[i] = static_cast<int8_t>(v); break;
+    case DataType::INT16: static_cast<int16_t*>(dst)[i] = static_cast<int16_t>(v); break;
+    case DataType::INT32: static_cast<int32_t*>(dst)[i] = static_cast<int32_t>(v); break;
+    case DataType::INT64: static_cast<int64_t*>(dst)[i] = static_cast<int64_t>(v); break;
+    case DataType::BFLOAT16: static_cast<bfloat16*>(dst)[i] = bfloat16(static_cast<float>(v)); break;
+    case DataType::FLOAT16: static_cast<float16*>(dst)[i] = float16(static_cast<float>(v)); break;
+    case DataType::FLOAT32: static_cast<float*>(dst)[i] = static_cast<float>(v); break;
+    case DataType::FLOAT64: static_cast<double*>(dst)[i] = v; break;
+  }
+}
+}  // namespace
+
+static Metadata make_meta(std::vector<int64_t> shape, DataType dtype, Device device) {
+  if (shape.empty()) throw std::runtime_error("Tensor shape cannot be empty");
+  Metadata m;
+  m.numel = calc_numel(shape);
+  m.shape = std::move(shape);
+  m.dtype = dtype;
+  m.device = device;
+  m.calculate_strides();
+  return m;
+}
+
+Tensor tvhost::adopt(std::vector<int64_t> shape, DataType dtype, std::shared_ptr<TensorImpl> impl, Device device) {
+  Tensor t;
+  t.m_meta = make_meta(std::move(shape), dtype, device);
+  if (!impl || impl->numel() != t.m_meta.numel) throw std::runtime_error("adopt: storage does not match the shape");
+  t.m_impl = std::move(impl);
+  return t;
+}
+
+Tensor::Tensor(std::vector<int64_t> shape, DataType dtype, Device device)
+    : m_meta(make_meta(std::move(shape), dtype, device)) {
+  m_impl = create_tensor_impl(m_meta.numel, dtype, device);
+}
+Tensor::Tensor(std::initializer_list<int64_t> shape, DataType dtype, Device device)
+    : Tensor(std::vector<int64_t>(shape), dtype, device) {}
+Tensor::Tensor(std::vector<int64_t> shape, DataType dtype) : Tensor(std::move(shape), dtype, kDefaultDevice) {}
+Tensor::Tensor(std::initializer_list<int64_t> shape, DataType dtype)
+    : Tensor(std::vector<int64_t>(shape), dtype, kDefaultDevice) {}
+
+Tensor::Tensor(void* ptr, std::vector<int64_t> shape, DataType dtype, Device device) {
+  if (shape.empty()) throw std::runtime_error("Tensor shape cannot be empty");
+  if (ptr == nullptr) throw std::runtime_error("ptr can not nullptr");
+  m_meta = make_meta(std::move(shape), dtype, device);
+  m_impl = create_tensor_impl(ptr, m_meta.numel, dtype, device);
+}
+
+Tensor::Tensor(const Tensor& other) : m_meta(other.m_meta) {
+  m_meta.offset = 0;
+  m_meta.calculate_strides();
+  m_impl = other.m_impl ? std::shared_ptr<TensorImpl>(other.m_impl->clone()) : nullptr;
+}
+Tensor& Tensor::operator=(const Tensor& other) {
+  if (this != &other) {
+    Tensor copy(other);
+    *this = std::move(copy);
+  }
+  return *this;
+}
+
+void* Tensor::data() { return m_impl ? m_impl->data() : nullptr; }
+const void* Tensor::data() const { return m_impl ? m_impl->data() : nullptr; }
+
+int64_t Tensor::shape(int i) const {
+  const int n = static_cast<int>(m_meta.shape.size());
+  if (i < 0) i += n;
+  if (i < 0 || i >= n) throw std::out_of_range("shape index out of range");
+  return m_meta.shape[static_cast<size_t>(i)];
+}
+
+Tensor Tensor::clone() const { return Tensor(*this); }
+
+void Tensor::to_host() {
+  if (m_meta.device == Device::CPU) return;
+  auto host = create_tensor_impl(m_meta.numel, m_meta.dtype, Device::CPU);
+  copy_device_to_host(m_impl, host, m_meta.dtype);
+  m_impl = host;
+  m_meta.device = Device::CPU;
+}
+
+void Tensor::to_device(uint32_t id) {
+  if (m_meta.device != Device::CPU) return;
+  auto dev = std::make_shared<tvhost::CudaStorage>(nullptr, m_meta.numel, m_meta.dtype,
+                                                   tvhost::cuda_context(static_cast<int>(id)));
+  copy_host_to_device(m_impl, dev, m_meta.dtype);
+  m_impl = dev;
+  m_meta.device = Device::CUDA;
+}
+
+void Tensor::read_element(size_t index, void* out) const {
+  const size_t es = calc_dtype_size(m_meta.dtype);
+  if (m_meta.device == Device::CPU) {
+    std::memcpy(out, static_cast<const char*>(m_impl->data()) + index * es, es);
+    return;
+  }
+  auto s = std::dynamic_pointer_cast<tvhost::CudaStorage>(m_impl);
+  tvhost::check(tvb_memcpy_d2h(s->cuda()->device(), out, static_cast<const char*>(s->data()) + index * es, es, nullptr),
+                "tvb_memcpy_d2h");
+  s->cuda()->wait();
+}
+
+// ---- creation helpers ----------------------------------------------------------------------
+static Tensor from_host_values(const std::vector<int64_t>& shape, DataType dtype, auto&& value_at) {
+  const size_t n = calc_numel(shape);
+  std::vector<char> buf(n * calc_dtype_size(dtype));
+  for (size_t i = 0; i < n; ++i) store_value(buf.data(), i, dtype, value_at(i));
+  return Tensor(buf.data(), shape, dtype, kDefaultDevice);
+}
+
+void Tensor::ManualSeed(uint64_t seed) {
+  std::lock_guard<std::mutex> g(g_rng_mu);
+  rng().seed(seed);
+}
+
+namespace ops {
+Tensor Fill(const std::vector<int64_t>& shape, DataType dtype, float value) {
+  return from_host_values(shape, dtype, [&](size_t) { return static_cast<double>(value); });
+}
+Tensor Zeros(const std::vector<int64_t>& shape, DataType dtype) { return Fill(shape, dtype, 0.0f); }
+Tensor Ones(const std::vector<int64_t>& shape, DataType dtype) { return Fill(shape, dtype, 1.0f); }
+// Uniform in [min, max): real-valued for float dtypes, whole numbers in [min, max] for integer
+// dtypes (the distributions of the reference's CPU initialiser, src/backend/cpu/initializer.cpp:27-32).
+Tensor Random(const std::vector<int64_t>& shape, DataType dtype, float min, float max) {
+  std::lock_guard<std::mutex> g(g_rng_mu);
+  if (dtype <= DataType::INT64) {
+    std::uniform_int_distribution<int64_t> d(static_cast<int64_t>(min), static_cast<int64_t>(max));
+    return from_host_values(shape, dtype, [&](size_t) { return static_cast<double>(d(rng())); });
+  }
+  std::uniform_real_distribution<double> d(min, max);
+  return from_host_values(shape, dtype, [&](size_t) { return d(rng()); });
+}
+}  // namespace ops
+
+Tensor Tensor::Zeros(std::vector<int64_t> shape, DataType dtype) { return ops::Zeros(shape, dtype); }
+Tensor Tensor::Ones(std::vector<int64_t> shape, DataType dtype) { return ops::Ones(shape, dtype); }
+Tensor Tensor::Fill(std::vector<int64_t> shape, float value, DataType dtype) { return ops::Fill(shape, dtype, value); }
+Tensor Tensor::Random(std::vector<int64_t> shape, float min, float max, DataType dtype) {
+  return ops::Random(shape, dtype, min, max);
+}
+Tensor Tensor::Random(std::initializer_list<int64_t> shape, float min, float max, DataType dtype) {
+  return ops::Random(std::vector<int64_t>(shape), dtype, min, max);
+}

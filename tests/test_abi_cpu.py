@@ -110,3 +110,18 @@ def test_oracle_is_not_reachable_from_the_product():
         if path.is_file() and path.suffix in {".py", ".cu", ".cuh", ".h", ".cpp", ".hpp"}:
             text = path.read_text(errors="ignore")
             assert "oracle" not in text.lower() and "refcheck" not in text, path
+
+
+def test_cpp_host_layer_builds_and_keeps_the_reference_symbols():
+    """The C++ layer exports ops::Mul and MulImpl<Device::CUDA>::execute under the same Itanium
+    names a build of the reference exports, so objects compiled against the reference's headers
+    for this path resolve against it."""
+    from tensorvia_b200 import build
+    lib = build.build_host_cpp()
+    out = subprocess.run(["nm", "-D", "--defined-only", str(lib)], capture_output=True, text=True, check=True).stdout
+    for sym in ("_ZN3ops3MulERK6TensorS2_",
+                "_ZN3ops7MulImplILN3via6DeviceE1EE7executeERK6TensorS6_",
+                "_Z20register_tensor_implN3via6DeviceESt8functionIFSt10shared_ptrI10TensorImplEPvmNS_8DataTypeEEE",
+                "_Z19copy_device_to_hostSt10shared_ptrI10TensorImplES1_N3via8DataTypeE"):
+        assert sym in out, sym
+    assert (lib.parent / "tv_mul_demo").exists() and (lib.parent / "tv_api_check").exists()

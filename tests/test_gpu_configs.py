@@ -257,3 +257,16 @@ def test_torch_facing_operator(tv):
     torch.cuda.synchronize()
     assert ch.dtype == torch.float32
     assert torch.allclose(ch, ai.float() @ bh.float(), rtol=1e-4, atol=1e-4)
+
+
+def test_cpp_host_layer_on_gpu(tv):
+    """The C++ Tensor / ops::Mul layer: its assertion program, and the reference's timing scenario."""
+    import subprocess
+    from tensorvia_b200 import build
+    lib = build.build_host_cpp()
+    out = subprocess.run([str(lib.parent / "tv_api_check")], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stdout + out.stderr
+    assert "all checks passed" in out.stdout
+    out = subprocess.run([str(lib.parent / "tv_mul_demo"), "5"], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stdout + out.stderr
+    assert out.stdout.count("Execution time:") == 5 and "avg times" in out.stdout
