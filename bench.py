@@ -127,13 +127,26 @@ def physical_gpu_index(local: int) -> int:
 # ---------------------------------------------------------------------------------------------
 # CPU arm: the reference's own ops::Mul (or the C restatement) on host cores
 # ---------------------------------------------------------------------------------------------
+def use_all_host_threads():
+    """torch.distributed.run exports OMP_NUM_THREADS=1 to its workers; the CPU arm is meant to use
+    the host's cores (the reference itself caps its matmul at 16 threads, mul.cpp:114)."""
+    n = os.cpu_count() or 1
+    os.environ["OMP_NUM_THREADS"] = str(n)
+    try:
+        C.CDLL("libgomp.so.1").omp_set_num_threads(n)
+    except OSError:
+        pass
+
+
 def load_cpu_impl():
     """-> (kind, matmul(a, b, dtype) -> seconds, threads).  Test infrastructure under oracle/ is
     executed here, and only here, as the CPU baseline."""
     sys.path.insert(0, str(ROOT / "tests"))
+    use_all_host_threads()
     import refcheck as R
     if R.have_ref():
         lib = R.ref()
+        use_all_host_threads()   # again, now that the library's OpenMP runtime is loaded
 
         def run(a, b, dt):
             t0 = time.perf_counter()
@@ -202,7 +215,7 @@ def reference_arm(args):
         "e2e": {"value": val, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
     return 0
 
 
@@ -373,14 +386,46 @@ def gpu_arm(args):
                                         "sample": sample + f", 1 run, {t:.2f} s", "host_cpus": os.cpu_count()}
             except Exception as e:  # the baseline must never take the GPU line down
                 line["cpu_baseline"] = {"value": None, "unit": unit, "cores": 0, "kind": "unavailable", "sample": str(e)[:200]}
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
     return 0
 
 
+class OneLineStdout:
+    """Routes file descriptor 1 to stderr while the benchmark runs (NCCL, the reference library
+    and others print banners to stdout) and hands back the real stdout for the one JSON line."""
+
+    def __enter__(self):
+        sys.stdout.flush()
+        self.real = os.dup(1)
+        os.dup2(2, 1)
+        return self
+
+    def emit(self, text: str):
+        os.write(self.real, (text + "\n").encode())
+
+    def __exit__(self, *exc):
+        sys.stdout.flush()
+        os.dup2(self.real, 1)
+        os.close(self.real)
+        return False
+
+
+OUT = None
+
+
+def emit(line: dict):
+    text = json.dumps(line)
+    if OUT is not None:
+        OUT.emit(text)
+    else:
+        print(text, flush=True)
+
+
 def main():
+    global OUT
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
@@ -389,14 +434,15 @@ def main():
     ap.add_argument("--impl", default="tensorvia_b200", choices=["tensorvia_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
-    if args.impl == "reference":
-        return reference_arm(args)
-    if args.gpus > 1 and "WORLD_SIZE" not in os.environ:
+    if args.gpus > 1 and "WORLD_SIZE" not in os.environ and args.impl != "reference":
         # convenience: relaunch under torch.distributed.run, one rank per GPU
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
                "--master-addr", "127.0.0.1", "--master-port", "29531", __file__] + sys.argv[1:]
         return subprocess.call(cmd)
-    return gpu_arm(args)
+    with OneLineStdout() as OUT:
+        if args.impl == "reference":
+            return reference_arm(args)
+        return gpu_arm(args)
 
 
 if __name__ == "__main__":

@@ -18,6 +18,7 @@
 #include "simt_gemm.cuh"
 #include "tvb.h"
 #include "umma_gemm.cuh"
+#include "umma_gemm_pair.cuh"
 
 namespace {
 
@@ -171,11 +172,16 @@ const SimtLaunch g_simt[8][8] = {TVB_SIMT_ROW(0), TVB_SIMT_ROW(1), TVB_SIMT_ROW(
 // ------------------------------------------------------------------------------------
 // tcgen05 dispatch
 // ------------------------------------------------------------------------------------
+constexpr int kPairStages = 3;   // stages of the CTA-pair kernel
+constexpr int kPairKAtoms = 2;   // 128-byte K atoms per stage of the CTA-pair kernel
+
 struct UmmaPlan {
   int op = -1;        // OP_*
   int block_n = 256;
   int stages = 4;
   int passes = 1;
+  bool pair = false;  // two CTAs (two SMs) per 256x256 tile, cta_group::2
+  int tile_m = 128;
   size_t es = 0;
   CUtensorMapDataType tm_type = CU_TENSOR_MAP_DATA_TYPE_UINT8;
 };
@@ -208,7 +214,18 @@ bool umma_eligible(int dta, int dtb, int64_t batch, int64_t M, int64_t K, int64_
     if (v == 128 || v == 256) p.block_n = v;
   }
   p.stages = (p.block_n == 256) ? 4 : 6;
-  const int64_t tiles = batch * ((M + 127) / 128) * ((N + p.block_n - 1) / p.block_n);
+  // CTA pairs once there are enough 256x256 tiles to occupy every pair of SMs; smaller
+  // problems keep one CTA per 128-row tile so that more SMs have work (TVB_CTA_PAIR overrides)
+  {
+    const int64_t pair_tiles = batch * ((M + 255) / 256) * ((N + 255) / 256);
+    p.pair = p.block_n == 256 && M > 128 && pair_tiles >= 74;
+    if (const char* e = getenv("TVB_CTA_PAIR")) p.pair = p.block_n == 256 && atoi(e) != 0;
+    if (p.pair) {
+      p.tile_m = 256;
+      p.stages = kPairStages;
+    }
+  }
+  const int64_t tiles = batch * ((M + p.tile_m - 1) / p.tile_m) * ((N + p.block_n - 1) / p.block_n);
   if (tiles > 0x7FFFFFFFll) return false;
   *plan = p;
   return true;
@@ -230,6 +247,59 @@ cudaError_t launch_umma_t(const CUtensorMap& a0, const CUtensorMap& a1, const CU
   umma_gemm_kernel<OP, BN, ST><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, s>>>(a0, a1, b0, b1, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError();
+}
+
+// CTA-pair kernel: clusters of two CTAs along the grid's x dimension
+template <int OP, int PST>
+cudaError_t launch_pair_st(const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b0,
+                          const CUtensorMap& b1, const UmmaGemmParams& p, int grid, cudaStream_t s) {
+  using Cfg = UmmaPairConfig<OP, PST, kPairKAtoms>;
+  static std::atomic<bool> configured[kMaxDevices];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!configured[dev].load(std::memory_order_acquire)) {
+    cudaError_t e = cudaFuncSetAttribute(umma_gemm_pair_kernel<OP, PST, kPairKAtoms>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    configured[dev].store(true, std::memory_order_release);
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+  cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  // The tile walk assumes every launched pair is resident at once; the driver knows how many
+  // clusters of this shape fit (a GPC with an odd SM count leaves one SM without a partner).
+  static std::atomic<int> max_clusters[kMaxDevices];
+  int fit = max_clusters[dev].load(std::memory_order_acquire);
+  if (fit == 0) {
+    int n = 0;
+    cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+    if (cudaOccupancyMaxActiveClusters(&n, umma_gemm_pair_kernel<OP, PST, kPairKAtoms>, &cfg) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = grid / 2;
+    }
+    fit = n;
+    max_clusters[dev].store(fit, std::memory_order_release);
+  }
+  if (grid / 2 > fit) cfg.gridDim = dim3(static_cast<unsigned>(2 * fit), 1, 1);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, umma_gemm_pair_kernel<OP, PST, kPairKAtoms>, a0, a1, b0, b1, p);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return e != cudaSuccess ? e : cudaGetLastError();
+}
+
+template <int OP>
+cudaError_t launch_pair_t(int stages, const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b0,
+                          const CUtensorMap& b1, const UmmaGemmParams& p, int grid, cudaStream_t s) {
+  (void)stages;
+  return launch_pair_st<OP, kPairStages>(a0, a1, b0, b1, p, grid, s);
 }
 
 template <int OP>
@@ -276,7 +346,9 @@ int ensure_workspace(Context* c, size_t bytes, cudaStream_t s) {
 int run_umma(Context* c, const UmmaPlan& plan, const void* A, const void* B, void* C, int64_t batch,
              int64_t M, int64_t K, int64_t N, cudaStream_t s) {
   const size_t es = plan.es;
-  const uint32_t bk = static_cast<uint32_t>(128 / es);
+  const uint32_t atom_k = static_cast<uint32_t>(128 / es);  // K elements per 128-byte swizzle atom
+  // K elements per pipeline stage, and the K rows of one MN-major B box
+  const uint32_t bk = plan.pair ? atom_k * kPairKAtoms : atom_k;
   const uint32_t chunk_n = static_cast<uint32_t>(128 / es);
   const void* a_hi = A;
   const void* b_hi = B;
@@ -316,12 +388,13 @@ int run_umma(Context* c, const UmmaPlan& plan, const void* A, const void* B, voi
 
   CUtensorMap ma0, ma1, mb0, mb1;
   int rc;
-  if ((rc = make_map(&ma0, plan.tm_type, es, a_hi, K, M, batch, bk, 128)) != TVB_OK) return rc;
-  if ((rc = make_map(&ma1, plan.tm_type, es, a_lo, K, M, batch, bk, 128)) != TVB_OK) return rc;
+  if ((rc = make_map(&ma0, plan.tm_type, es, a_hi, K, M, batch, atom_k, 128)) != TVB_OK) return rc;
+  if ((rc = make_map(&ma1, plan.tm_type, es, a_lo, K, M, batch, atom_k, 128)) != TVB_OK) return rc;
   if (plan.op == OP_TF32) {
     // B^T[batch][N][K]: boxes of block_n rows x 128 B of K
-    if ((rc = make_map(&mb0, plan.tm_type, es, b_hi, K, N, batch, bk, plan.block_n)) != TVB_OK) return rc;
-    if ((rc = make_map(&mb1, plan.tm_type, es, b_lo, K, N, batch, bk, plan.block_n)) != TVB_OK) return rc;
+    const uint32_t b_rows = plan.pair ? 128u : static_cast<uint32_t>(plan.block_n);  // a pair loads half each
+    if ((rc = make_map(&mb0, plan.tm_type, es, b_hi, K, N, batch, atom_k, b_rows)) != TVB_OK) return rc;
+    if ((rc = make_map(&mb1, plan.tm_type, es, b_lo, K, N, batch, atom_k, b_rows)) != TVB_OK) return rc;
   } else {
     if ((rc = make_map(&mb0, plan.tm_type, es, b_hi, N, K, batch, chunk_n, bk)) != TVB_OK) return rc;
     if ((rc = make_map(&mb1, plan.tm_type, es, b_lo, N, K, batch, chunk_n, bk)) != TVB_OK) return rc;
@@ -332,12 +405,12 @@ int run_umma(Context* c, const UmmaPlan& plan, const void* A, const void* B, voi
   p.N = static_cast<int32_t>(N);
   p.K = static_cast<int32_t>(K);
   p.batch = static_cast<int32_t>(batch);
-  p.m_tiles = static_cast<int32_t>((M + 127) / 128);
+  p.m_tiles = static_cast<int32_t>((M + plan.tile_m - 1) / plan.tile_m);
   p.n_tiles = static_cast<int32_t>((N + plan.block_n - 1) / plan.block_n);
   p.k_blocks = static_cast<int32_t>((K + bk - 1) / bk);
   p.passes = plan.passes;
-  // fp32: 8 stages = 256 elements of K per TMEM-resident partial sum (TVB_K_CHUNK overrides)
-  p.k_chunk_blocks = 8;
+  // fp32: 256 elements of K per TMEM-resident partial sum (TVB_K_CHUNK, in stages, overrides)
+  p.k_chunk_blocks = static_cast<int32_t>(256 / bk);
   if (const char* e = getenv("TVB_K_CHUNK")) {
     const int v = atoi(e);
     if (v >= 1 && v <= 4096) p.k_chunk_blocks = v;
@@ -349,6 +422,16 @@ int run_umma(Context* c, const UmmaPlan& plan, const void* A, const void* B, voi
   const int grid = static_cast<int>(p.total_tiles < static_cast<uint32_t>(c->sm_count) ? p.total_tiles
                                                                                        : c->sm_count);
   cudaError_t e;
+  if (plan.pair) {
+    const uint32_t pairs = static_cast<uint32_t>(c->sm_count / 2);
+    const int pgrid = 2 * static_cast<int>(p.total_tiles < pairs ? p.total_tiles : pairs);
+    switch (plan.op) {
+      case OP_F16: e = launch_pair_t<OP_F16>(plan.stages, ma0, ma1, mb0, mb1, p, pgrid, s); break;
+      case OP_BF16: e = launch_pair_t<OP_BF16>(plan.stages, ma0, ma1, mb0, mb1, p, pgrid, s); break;
+      case OP_TF32: e = launch_pair_t<OP_TF32>(plan.stages, ma0, ma1, mb0, mb1, p, pgrid, s); break;
+      default: e = launch_pair_t<OP_I8>(plan.stages, ma0, ma1, mb0, mb1, p, pgrid, s); break;
+    }
+  } else
   switch (plan.op) {
     case OP_F16: e = launch_umma_op<OP_F16>(plan.block_n, ma0, ma1, mb0, mb1, p, grid, s); break;
     case OP_BF16: e = launch_umma_op<OP_BF16>(plan.block_n, ma0, ma1, mb0, mb1, p, grid, s); break;
@@ -689,13 +772,18 @@ int tvb_matmul_plan(int device, int dta, int dtb, int64_t batch, int64_t M, int6
   if (algo == TVB_ALGO_TCGEN05 && !can) return fail(TVB_ERR_UNSUPPORTED, "problem is not eligible for the tcgen05 path");
   if (can && algo != TVB_ALGO_SIMT) {
     out->algo = TVB_ALGO_TCGEN05;
-    out->tile_m = 128;
+    out->tile_m = plan.tile_m;
     out->tile_n = plan.block_n;
-    out->tile_k = static_cast<int>(128 / plan.es);
+    out->tile_k = static_cast<int>(128 / plan.es) * (plan.pair ? kPairKAtoms : 1);
     out->stages = plan.stages;
     out->passes = plan.passes;
-    out->tiles = static_cast<uint64_t>(batch) * ((M + 127) / 128) * ((N + plan.block_n - 1) / plan.block_n);
-    out->ctas = static_cast<int>(out->tiles < static_cast<uint64_t>(c->sm_count) ? out->tiles : c->sm_count);
+    out->tiles = static_cast<uint64_t>(batch) * ((M + plan.tile_m - 1) / plan.tile_m) * ((N + plan.block_n - 1) / plan.block_n);
+    if (plan.pair) {
+      const uint64_t pairs = static_cast<uint64_t>(c->sm_count / 2);
+      out->ctas = 2 * static_cast<int>(out->tiles < pairs ? out->tiles : pairs);
+    } else {
+      out->ctas = static_cast<int>(out->tiles < static_cast<uint64_t>(c->sm_count) ? out->tiles : c->sm_count);
+    }
     if (plan.op == OP_TF32) {
       const size_t na = static_cast<size_t>(batch) * M * K, nb = static_cast<size_t>(batch) * K * N;
       out->workspace_bytes = 2 * ((na * 4 + 255) / 256 * 256) + 2 * ((nb * 4 + 255) / 256 * 256);

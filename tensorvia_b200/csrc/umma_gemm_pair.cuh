@@ -1,0 +1,317 @@
+// CTA-pair variant of the tcgen05 GEMM: two CTAs of a cluster (two SMs) compute one
+// 256 x 256 output tile with `tcgen05.mma.cta_group::2`.
+//
+// Why: with one CTA per tile every 128x256x16 MMA reads 12 KB of operands from its SM's shared
+// memory while TMA writes 48 KB per stage into it; together that is more than the shared
+// memory delivers in the time of the MMA, and the tensor pipe idles a quarter of the time
+// (measured: 72.6 % busy).  In a pair each SM holds its 128 rows of A and only HALF of the B
+// tile (128 of the 256 columns); the tensor cores of both SMs read both halves.  Per SM and
+// stage that is 32 KB written and 8 KB read per MMA instead of 48 KB and 12 KB.
+//
+// A stage holds KATOMS x 128 bytes of K (KATOMS = 2: eight MMAs per stage, three stages of
+// 64 KB).  A pipeline microbenchmark on B200 showed the tensor pipe losing about 64 cycles at
+// every stage hand-over when a stage carries four MMAs (144 cycles per 128-cycle MMA whatever
+// the stage count, copy count or bytes), and none with eight (128.1).
+//
+// Roles per CTA are those of umma_gemm_kernel (warp 0 TMA producer, warp 1 TMEM + MMA, warps
+// 2.. epilogue) with these differences:
+//   * both producers load (own A rows, own B columns) and count their bytes on the LEADER's
+//     (even CTA's) full barrier; only the leader's producer posts the expected byte count;
+//   * only the leader's warp 1 issues MMAs; its commits arrive on the barriers of BOTH CTAs
+//     (stage free, accumulator ready);
+//   * epilogue warps of both CTAs read their own TMEM (rows rank*128 .. +127 of the tile) and
+//     arrive on the leader's accumulator-free barrier;
+//   * TMEM is allocated and freed with the cta_group::2 forms by warp 1 of both CTAs, and the
+//     cluster synchronises before either CTA leaves.
+// No load uses multicast: each CTA fetches exactly the bytes it keeps.
+// Every wait is bounded as in the single-CTA kernel.
+#pragma once
+#include "umma_gemm.cuh"
+
+namespace tvb {
+
+template <int OP, int STAGES, int KATOMS>
+struct UmmaPairConfig {
+  static constexpr int BLOCK_M = 256;         // per pair; 128 rows per CTA
+  static constexpr int BLOCK_N = 256;         // per pair; each CTA loads 128 columns of B
+  static constexpr int A_BYTES = 128 * 128 * KATOMS;   // per CTA and stage
+  static constexpr int B_BYTES = 128 * 128 * KATOMS;   // per CTA and stage (half of the B tile)
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int NUM_BARRIERS = 2 * STAGES + 4;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + NUM_BARRIERS * 8 + 16 + 1024;
+  static constexpr int TMEM_COLS = 2 * BLOCK_N;
+  static constexpr int EPI_WARPS = UmmaEpilogue<OP>::WARPS;
+  static constexpr int THREADS = 64 + 32 * EPI_WARPS;
+};
+
+// p.m_tiles counts 256-row tiles here; everything else as in UmmaGemmParams.
+template <int OP, int STAGES, int KATOMS>
+__global__ void __launch_bounds__(64 + 32 * UmmaEpilogue<OP>::WARPS, 1)
+umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
+                      const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
+                      const UmmaGemmParams p) {
+  using T = OpTraits<OP>;
+  using Cfg = UmmaPairConfig<OP, STAGES, KATOMS>;
+  using Out = typename T::Out;
+  constexpr bool CHUNKED = UmmaEpilogue<OP>::CHUNKED;
+  constexpr int ES = T::ES;
+  constexpr int BLOCK_N = Cfg::BLOCK_N;
+  constexpr int HALF_B = 128;                    // B columns this CTA loads
+  constexpr int ATOM_K = 128 / ES;               // K elements in one 128-byte swizzle atom
+  constexpr int BK = KATOMS * ATOM_K;            // K elements per stage
+  constexpr int ATOM_BYTES = 128 * 128;          // 128 rows x 128 B: one K-major tile of one atom
+  constexpr int CHUNK_N = 128 / ES;              // N elements per 128-byte B box (MN-major)
+  constexpr int NCHUNK = HALF_B / CHUNK_N;       // B boxes per CTA and stage
+  constexpr int CHUNK_BYTES = BK * 128;          // one MN-major box: BK k-rows x 128 B
+  constexpr int KSTEPS = 4 * KATOMS;
+  constexpr int B_KSTEP_BYTES = (32 / ES) * 128;
+  constexpr bool B_MN = T::B_MN_MAJOR != 0;
+  constexpr uint32_t IDESC = ptx::make_instr_desc(T::D_FMT, T::AB_FMT, 0u, T::B_MN_MAJOR, 256, BLOCK_N);
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  const uint32_t bar_base = base + STAGES * Cfg::STAGE_BYTES;
+  auto a_smem = [&](int s) { return base + s * Cfg::STAGE_BYTES; };
+  auto b_smem = [&](int s) { return base + s * Cfg::STAGE_BYTES + Cfg::A_BYTES; };
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
+  auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
+  const uint32_t slot_addr = bar_base + 8u * Cfg::NUM_BARRIERS;
+  volatile uint32_t* slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (slot_addr - raw_addr));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = ptx::cluster_cta_rank();   // 0 = leader
+  const bool leader = rank == 0;
+  // the leader's copies of the barriers both CTAs signal, as cluster-wide addresses
+  const uint32_t leader_bar_base = ptx::map_to_cta(bar_base, 0);
+  auto full_bar_leader = [&](int s) { return leader_bar_base + 8u * s; };
+  auto tempty_bar_leader = [&](int b) { return leader_bar_base + 8u * (2 * STAGES + 2 + b); };
+  const uint32_t pair = blockIdx.x >> 1;
+  const uint32_t num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(full_bar(s), 1);    // leader's copy: its producer's arrive + bytes of both CTAs
+      ptx::mbar_init(empty_bar(s), 1);   // one commit from the leader's MMA thread
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(tfull_bar(b), 1);
+      ptx::mbar_init(tempty_bar(b), 2 * Cfg::EPI_WARPS);  // leader's copy: one arrival per epilogue warp of the pair
+    }
+    ptx::fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    ptx::prefetch_tmap(&tmA0);
+    ptx::prefetch_tmap(&tmB0);
+    if (p.passes > 1) {
+      ptx::prefetch_tmap(&tmA1);
+      ptx::prefetch_tmap(&tmB1);
+    }
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc_pair(slot_addr, Cfg::TMEM_COLS);
+    ptx::tmem_relinquish_pair();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::cluster_sync_all();   // both CTAs' barriers exist before anything arrives on them remotely
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *slot_ptr;
+
+  const int kc = CHUNKED ? p.k_chunk_blocks : p.k_blocks;
+  const int chunks = (p.k_blocks + kc - 1) / kc;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (uint32_t tile = pair; ok && tile < p.total_tiles; tile += num_pairs) {
+        int b, mt, nt;
+        decode_tile(tile, p, b, mt, nt);
+        const int row0 = mt * Cfg::BLOCK_M + static_cast<int>(rank) * 128;
+        const int col0 = nt * BLOCK_N + static_cast<int>(rank) * HALF_B;
+        for (int kb = 0; ok && kb < p.k_blocks; ++kb) {
+          for (int pass = 0; pass < p.passes; ++pass) {
+            if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, p.wait_limit_ns)) {
+              atomicOr(p.status, ST_PRODUCER_TIMEOUT);
+              ok = false;
+              break;
+            }
+            const CUtensorMap* ma = (p.passes > 1 && pass == 0) ? &tmA1 : &tmA0;
+            const CUtensorMap* mb = (p.passes > 1 && pass == 1) ? &tmB1 : &tmB0;
+            if (leader) ptx::mbar_expect_tx(full_bar(stage), 2 * Cfg::STAGE_BYTES);
+#pragma unroll
+            for (int j = 0; j < KATOMS; ++j)
+              ptx::tma_load_3d_pair(a_smem(stage) + j * ATOM_BYTES, ma, full_bar_leader(stage),
+                                    kb * BK + j * ATOM_K, row0, b);
+            if constexpr (B_MN) {
+#pragma unroll
+              for (int c = 0; c < NCHUNK; ++c)
+                ptx::tma_load_3d_pair(b_smem(stage) + c * CHUNK_BYTES, mb, full_bar_leader(stage),
+                                      col0 + c * CHUNK_N, kb * BK, b);
+            } else {
+#pragma unroll
+              for (int j = 0; j < KATOMS; ++j)
+                ptx::tma_load_3d_pair(b_smem(stage) + j * ATOM_BYTES, mb, full_bar_leader(stage),
+                                      kb * BK + j * ATOM_K, col0, b);
+            }
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader only)
+    if (lane == 0 && leader) {
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t local = 0;
+      bool ok = true;
+      for (uint32_t tile = pair; ok && tile < p.total_tiles; tile += num_pairs) {
+        for (int ch = 0; ok && ch < chunks; ++ch, ++local) {
+          const uint32_t buf = local & 1u;
+          const uint32_t acc_phase = (local >> 1) & 1u;
+          if (!ptx::mbar_wait(tempty_bar(buf), acc_phase ^ 1u, p.wait_limit_ns)) {
+            atomicOr(p.status, ST_MMA_TIMEOUT);
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t d_tmem = tmem_base + buf * BLOCK_N;
+          const int kb_end = min(p.k_blocks, (ch + 1) * kc);
+          const int k_iters = (kb_end - ch * kc) * p.passes;
+          for (int it = 0; it < k_iters; ++it) {
+            if (!ptx::mbar_wait(full_bar(stage), phase, p.wait_limit_ns)) {
+              atomicOr(p.status, ST_MMA_TIMEOUT);
+              ok = false;
+              break;
+            }
+            ptx::tc_fence_after();
+            const uint32_t a0 = a_smem(stage);
+            const uint32_t b0 = b_smem(stage);
+#pragma unroll
+            for (int k = 0; k < KSTEPS; ++k) {
+              const uint32_t koff = (k >> 2) * ATOM_BYTES + (k & 3) * 32;  // atom, then 32 B steps inside it
+              const uint64_t adesc = ptx::make_smem_desc(a0 + koff, 16, 1024);
+              const uint64_t bdesc = B_MN ? ptx::make_smem_desc(b0 + k * B_KSTEP_BYTES, CHUNK_BYTES, 1024)
+                                          : ptx::make_smem_desc(b0 + koff, 16, 1024);
+              ptx::tc_mma_pair<T::MMA>(d_tmem, adesc, bdesc, IDESC, (it > 0 || k > 0) ? 1u : 0u);
+            }
+            ptx::tc_commit_pair(empty_bar(stage), 3);  // stage free in both CTAs
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+          if (ok) ptx::tc_commit_pair(tfull_bar(buf), 3);  // accumulator ready in both CTAs
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (both CTAs)
+    const int quad = warp & 3;
+    uint32_t local = 0;
+    bool ok = true;
+    Out* const Cbase = reinterpret_cast<Out*>(p.C);
+    if constexpr (!CHUNKED) {
+      for (uint32_t tile = pair; ok && tile < p.total_tiles; tile += num_pairs, ++local) {
+        int b, mt, nt;
+        decode_tile(tile, p, b, mt, nt);
+        const uint32_t buf = local & 1u;
+        const uint32_t acc_phase = (local >> 1) & 1u;
+        const bool landed = ptx::mbar_wait(tfull_bar(buf), acc_phase, p.wait_limit_ns);
+        if (!__all_sync(0xffffffffu, landed)) {
+          if (lane == 0) atomicOr(p.status, ST_EPILOGUE_TIMEOUT);
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after();
+        const int row = mt * Cfg::BLOCK_M + static_cast<int>(rank) * 128 + quad * 32 + lane;
+        const int col0 = nt * BLOCK_N;
+        const uint32_t taddr = tmem_base + buf * BLOCK_N + (static_cast<uint32_t>(quad * 32) << 16);
+        Out* crow = Cbase + (static_cast<size_t>(b) * p.M + static_cast<size_t>(row)) * p.N + col0;
+#pragma unroll 1
+        for (int c = 0; c < BLOCK_N / 32; ++c) {
+          uint32_t v[32];
+          ptx::tmem_ld_32x32(taddr + c * 32, v);
+          ptx::tmem_ld_wait();
+          const int cols_left = p.N - (col0 + c * 32);
+          if (row < p.M && cols_left > 0) store_row_chunk<OP>(crow + c * 32, v, cols_left);
+        }
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive_cluster(tempty_bar_leader(buf));
+      }
+    } else {
+      constexpr int HALF_N = BLOCK_N / 2;
+      const int half = (warp - 2) >> 2;
+      float acc[HALF_N];
+      for (uint32_t tile = pair; ok && tile < p.total_tiles; tile += num_pairs) {
+        int b, mt, nt;
+        decode_tile(tile, p, b, mt, nt);
+#pragma unroll
+        for (int j = 0; j < HALF_N; ++j) acc[j] = 0.f;
+        for (int ch = 0; ch < chunks; ++ch, ++local) {
+          const uint32_t buf = local & 1u;
+          const uint32_t acc_phase = (local >> 1) & 1u;
+          const bool landed = ptx::mbar_wait(tfull_bar(buf), acc_phase, p.wait_limit_ns);
+          if (!__all_sync(0xffffffffu, landed)) {
+            if (lane == 0) atomicOr(p.status, ST_EPILOGUE_TIMEOUT);
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t taddr = tmem_base + buf * BLOCK_N + half * HALF_N +
+                                 (static_cast<uint32_t>(quad * 32) << 16);
+#pragma unroll
+          for (int c = 0; c < HALF_N / 32; ++c) {
+            uint32_t v[32];
+            ptx::tmem_ld_32x32(taddr + c * 32, v);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) acc[c * 32 + j] += __uint_as_float(v[j]);
+          }
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive_cluster(tempty_bar_leader(buf));
+        }
+        if (!ok) break;
+        const int row = mt * Cfg::BLOCK_M + static_cast<int>(rank) * 128 + quad * 32 + lane;
+        const int col0 = nt * BLOCK_N + half * HALF_N;
+        if (row < p.M) {
+          float4* crow = reinterpret_cast<float4*>(
+              reinterpret_cast<float*>(Cbase) +
+              (static_cast<size_t>(b) * p.M + static_cast<size_t>(row)) * p.N + col0);
+#pragma unroll
+          for (int g = 0; g < HALF_N / 4; ++g)
+            if (col0 + g * 4 < p.N)
+              crow[g] = make_float4(acc[4 * g], acc[4 * g + 1], acc[4 * g + 2], acc[4 * g + 3]);
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1 && *reinterpret_cast<volatile uint32_t*>(p.status) != 0) {
+    // after a timeout: give loads that were issued but never consumed a bounded moment to land
+    const uint64_t t0 = ptx::globaltimer_ns();
+    while (ptx::globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  ptx::cluster_sync_all();   // the peer may still arrive on this CTA's barriers until here
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+}  // namespace tvb

@@ -119,7 +119,11 @@ def test_auto_falls_back_when_pitch_is_not_16_bytes(dev, tv):
         dev.matmul(A, R.BFLOAT16, B, R.BFLOAT16, algo=TCGEN05)
     assert e.value.code == 9
     info = tv.ops.plan(R.BFLOAT16, R.BFLOAT16, 1, 4096, 4096, 4096)
-    assert (info.algo, info.tile_m, info.tile_n, info.tile_k, info.passes) == (TCGEN05, 128, 256, 64, 1)
+    # large problems run on CTA pairs (256 x 256 tiles, 128 elements of K per stage) ...
+    assert (info.algo, info.tile_m, info.tile_n, info.tile_k, info.passes) == (TCGEN05, 256, 256, 128, 1)
+    # ... small ones keep one CTA per 128-row tile so that more SMs have work
+    info = tv.ops.plan(R.BFLOAT16, R.BFLOAT16, 1, 1024, 1024, 1024)
+    assert (info.algo, info.tile_m, info.tile_n, info.tile_k) == (TCGEN05, 128, 256, 64)
     info = tv.ops.plan(R.FLOAT32, R.FLOAT32, 1, 2592, 2048, 4096)
     assert info.algo == TCGEN05 and info.passes == 3 and info.workspace_bytes > 0
 
