@@ -330,6 +330,12 @@ def gpu_arm(args):
     check(lib.tvb_memcpy_d2h(local, dev_c.ctypes.data, sets[0][2], dev_c.nbytes, None))
     check(lib.tvb_sync(local))
     e2e_same = bool((host_c == dev_c).all())
+    if not e2e_same and dt == F32:
+        # the host call multiplies row slabs, which may run on the single-CTA kernel while the
+        # whole problem runs on CTA pairs; the two interleave the three TF32 passes at different
+        # K granularity and differ in the last bits of fp32
+        hf, df = host_c.view(np.float32).astype(np.float64), dev_c.view(np.float32).astype(np.float64)
+        e2e_same = bool(np.linalg.norm(hf - df) <= 1e-5 * np.linalg.norm(df))
     for p in (ha, hb, hc):
         check(lib.tvb_host_free(p))
 

@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 #include <cudaTypedefs.h>
 
+#include <algorithm>
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
@@ -62,6 +63,12 @@ struct Context {
   void* ws = nullptr;
   size_t ws_bytes = 0;
   cudaEvent_t ws_event = nullptr;
+  // copy streams and events of the pipelined host-buffer call (tvb_matmul_host)
+  static constexpr int kMaxSlabs = 16;
+  cudaStream_t copy_in = nullptr, copy_out = nullptr;
+  cudaEvent_t ev_in[kMaxSlabs + 1] = {};   // [0] = B landed, [1+i] = slab i of A landed
+  cudaEvent_t ev_done[kMaxSlabs] = {};     // slab i of C computed
+  cudaEvent_t ev_out = nullptr;            // all of C is back on the host
   bool ws_used = false;
   std::mutex mu;
 };
@@ -601,6 +608,11 @@ int tvb_init(int device) {
   c->sm_count = prop.multiProcessorCount;
   TVB_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
   TVB_CUDA(cudaEventCreateWithFlags(&c->ws_event, cudaEventDisableTiming));
+  TVB_CUDA(cudaStreamCreateWithFlags(&c->copy_in, cudaStreamNonBlocking));
+  TVB_CUDA(cudaStreamCreateWithFlags(&c->copy_out, cudaStreamNonBlocking));
+  for (auto& e : c->ev_in) TVB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+  for (auto& e : c->ev_done) TVB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+  TVB_CUDA(cudaEventCreateWithFlags(&c->ev_out, cudaEventDisableTiming));
   TVB_CUDA(cudaMalloc(&c->d_status, sizeof(uint32_t)));
   TVB_CUDA(cudaMemset(c->d_status, 0, sizeof(uint32_t)));
   TVB_CUDA(cudaHostAlloc(&c->h_status, sizeof(uint32_t), cudaHostAllocDefault));
@@ -622,6 +634,13 @@ int tvb_shutdown(void) {
     cudaFree(c->d_status);
     cudaFreeHost(c->h_status);
     cudaEventDestroy(c->ws_event);
+    for (auto& e : c->ev_in) cudaEventDestroy(e);
+    for (auto& e : c->ev_done) cudaEventDestroy(e);
+    cudaEventDestroy(c->ev_out);
+    cudaStreamSynchronize(c->copy_in);
+    cudaStreamSynchronize(c->copy_out);
+    cudaStreamDestroy(c->copy_in);
+    cudaStreamDestroy(c->copy_out);
     cudaStreamDestroy(c->stream);
     delete c;
     g_ctx[d] = nullptr;
@@ -822,10 +841,65 @@ int tvb_matmul_host(int device, const void* hA, const void* hB, void* hC, int dt
     cleanup();
     return rc;
   }
-  rc = tvb_memcpy_h2d(device, dA, hA, ba, nullptr);
-  if (rc == TVB_OK) rc = tvb_memcpy_h2d(device, dB, hB, bb, nullptr);
-  if (rc == TVB_OK) rc = matmul_impl(device, dA, dB, dC, dta, dtb, dtc, batch, M, K, N, nullptr, TVB_ALGO_AUTO);
-  if (rc == TVB_OK) rc = tvb_memcpy_d2h(device, hC, dC, bc, nullptr);
+  // Pipeline over slabs of A's rows (2-D) or runs of batches (3-D): B goes in first, then
+  // slab i of A is copied in while slab i-1 is multiplied and slab i-2 of C is copied out.
+  // Host->device and device->host copies use the two directions of the link at once, so a
+  // call costs about max(bytes in, bytes out) instead of their sum.  Pageable host memory
+  // works too (the driver stages it), it just does not overlap.
+  DeviceGuard guard(device);
+  const int64_t units = batch > 1 ? batch : M;            // what is cut into slabs
+  const int64_t granule = batch > 1 ? 1 : 256;            // whole CTA-pair tiles per slab
+  // about 1024 rows (or one batch) per slab: long enough copies to run the link at full rate,
+  // short enough that the first product starts early (measured best on 4096^3: 4 slabs)
+  int nslabs = static_cast<int>(std::min<int64_t>(Context::kMaxSlabs, batch > 1 ? batch : std::max<int64_t>(1, M / 1024)));
+  if (ba + bc < (size_t(8) << 20)) nslabs = 1;            // too small to be worth cutting
+  if (const char* e = getenv("TVB_HOST_SLABS")) {
+    const int v = atoi(e);
+    if (v >= 1 && v <= Context::kMaxSlabs) nslabs = std::min<int>(v, static_cast<int>((units + granule - 1) / granule));
+  }
+  const size_t es_a = dtype_size(dta), es_b = dtype_size(dtb), es_c = dtype_size(dtc);
+  auto cu = [&](cudaError_t e, const char* what) {
+    if (e != cudaSuccess && rc == TVB_OK) rc = fail(TVB_ERR_CUDA, "%s failed: %s", what, cudaGetErrorString(e));
+  };
+  // the copy streams start after whatever the caller queued on the library's stream
+  cu(cudaEventRecord(c->ev_out, c->stream), "cudaEventRecord");
+  cu(cudaStreamWaitEvent(c->copy_in, c->ev_out, 0), "cudaStreamWaitEvent");
+  cu(cudaStreamWaitEvent(c->copy_out, c->ev_out, 0), "cudaStreamWaitEvent");
+  if (batch == 1) {
+    cu(cudaMemcpyAsync(dB, hB, bb, cudaMemcpyHostToDevice, c->copy_in), "cudaMemcpyAsync(B)");
+    cu(cudaEventRecord(c->ev_in[0], c->copy_in), "cudaEventRecord");
+    cu(cudaStreamWaitEvent(c->stream, c->ev_in[0], 0), "cudaStreamWaitEvent");
+  }
+  for (int i = 0; i < nslabs && rc == TVB_OK; ++i) {
+    int64_t begin = 0, count = 0;
+    tvb_shard_range(units, granule, nslabs, i, &begin, &count);
+    if (count == 0) continue;
+    const int64_t sb = batch > 1 ? count : 1, sm = batch > 1 ? M : count;
+    const size_t a_off = static_cast<size_t>(begin) * (batch > 1 ? M * K : K) * es_a;
+    const size_t c_off = static_cast<size_t>(begin) * (batch > 1 ? M * N : N) * es_c;
+    const size_t b_off = batch > 1 ? static_cast<size_t>(begin) * K * N * es_b : 0;
+    if (batch > 1)
+      cu(cudaMemcpyAsync(static_cast<char*>(dB) + b_off, static_cast<const char*>(hB) + b_off,
+                         static_cast<size_t>(count) * K * N * es_b, cudaMemcpyHostToDevice, c->copy_in),
+         "cudaMemcpyAsync(B)");
+    cu(cudaMemcpyAsync(static_cast<char*>(dA) + a_off, static_cast<const char*>(hA) + a_off,
+                       static_cast<size_t>(sb) * sm * K * es_a, cudaMemcpyHostToDevice, c->copy_in),
+       "cudaMemcpyAsync(A)");
+    cu(cudaEventRecord(c->ev_in[1 + i], c->copy_in), "cudaEventRecord");
+    cu(cudaStreamWaitEvent(c->stream, c->ev_in[1 + i], 0), "cudaStreamWaitEvent");
+    if (rc == TVB_OK)
+      rc = matmul_impl(device, static_cast<char*>(dA) + a_off, static_cast<char*>(dB) + b_off,
+                       static_cast<char*>(dC) + c_off, dta, dtb, dtc, sb, sm, K, N, nullptr, TVB_ALGO_AUTO);
+    cu(cudaEventRecord(c->ev_done[i], c->stream), "cudaEventRecord");
+    cu(cudaStreamWaitEvent(c->copy_out, c->ev_done[i], 0), "cudaStreamWaitEvent");
+    cu(cudaMemcpyAsync(static_cast<char*>(hC) + c_off, static_cast<char*>(dC) + c_off,
+                       static_cast<size_t>(sb) * sm * N * es_c, cudaMemcpyDeviceToHost, c->copy_out),
+       "cudaMemcpyAsync(C)");
+  }
+  // the library's stream ends after the last copy out, so tvb_sync below covers everything
+  cu(cudaEventRecord(c->ev_out, c->copy_out), "cudaEventRecord");
+  cu(cudaStreamWaitEvent(c->stream, c->ev_out, 0), "cudaStreamWaitEvent");
+  cudaStreamSynchronize(c->copy_in);
   const int rs = tvb_sync(device);  // also drains the stream before the blocks go back to the pool
   cleanup();
   return rc != TVB_OK ? rc : rs;

@@ -239,12 +239,15 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_con
         const uint32_t taddr = tmem_base + buf * BLOCK_N + (static_cast<uint32_t>(quad * 32) << 16);
         Out* crow = Cbase + (static_cast<size_t>(b) * p.M + static_cast<size_t>(row)) * p.N + col0;
 #pragma unroll 1
-        for (int c = 0; c < BLOCK_N / 32; ++c) {
-          uint32_t v[32];
-          ptx::tmem_ld_32x32(taddr + c * 32, v);
+        for (int c = 0; c < BLOCK_N / 64; ++c) {
+          // two 32-column loads in flight per wait: half as many TMEM round trips
+          uint32_t v0[32], v1[32];
+          ptx::tmem_ld_32x32(taddr + c * 64, v0);
+          ptx::tmem_ld_32x32(taddr + c * 64 + 32, v1);
           ptx::tmem_ld_wait();
-          const int cols_left = p.N - (col0 + c * 32);
-          if (row < p.M && cols_left > 0) store_row_chunk<OP>(crow + c * 32, v, cols_left);
+          const int cols_left = p.N - (col0 + c * 64);
+          if (row < p.M && cols_left > 0) store_row_chunk<OP>(crow + c * 64, v0, cols_left);
+          if (row < p.M && cols_left > 32) store_row_chunk<OP>(crow + c * 64 + 32, v1, cols_left - 32);
         }
         ptx::tc_fence_before();
         __syncwarp();
