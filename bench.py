@@ -53,8 +53,8 @@ WORKLOAD_TEXT = {
     "c5": "fp32 A[65536,4096] @ B[4096,4096] -> fp32 (3xTF32 on tcgen05)",
 }
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the
-# ncu captures summarised under profiles/ (None until a capture exists for the workload)
-NCU_TRAFFIC_BYTES = {"c2": None}
+# ncu captures summarised under profiles/ (absent = no capture of that workload yet)
+NCU_TRAFFIC_BYTES = {"c2": 100.7e6}  # profiles/umma_gemm_pair_bf16_4096x4096x4096.md: 84.6 MB read + 16.1 MB written
 L2_BYTES = 126 * 1024 * 1024
 
 
