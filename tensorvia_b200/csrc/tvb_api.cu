@@ -69,7 +69,13 @@ struct Context {
   cudaEvent_t ev_in[kMaxSlabs + 1] = {};   // [0] = B landed, [1+i] = slab i of A landed
   cudaEvent_t ev_done[kMaxSlabs] = {};     // slab i of C computed
   cudaEvent_t ev_out = nullptr;            // all of C is back on the host
+  // shared-tile (split K) bookkeeping of the CTA-pair kernel: one flag per (tile, share, CTA,
+  // row quarter), written with a per-launch epoch so that it never needs clearing
+  static constexpr int kMaxFlags = 2048;
+  uint32_t* d_flags = nullptr;
+  uint32_t sk_epoch = 0;
   bool ws_used = false;
+  cudaStream_t ws_stream = nullptr;   // stream of the scratch's last user
   std::mutex mu;
 };
 
@@ -257,6 +263,48 @@ cudaError_t launch_umma_t(const CUtensorMap& a0, const CUtensorMap& a1, const CU
 }
 
 // CTA-pair kernel: clusters of two CTAs along the grid's x dimension
+// How many CTA pairs of this kernel the device holds at once (the tile walk assumes every
+// launched pair is resident; a GPC with an odd SM count leaves one SM without a partner).
+template <int OP, int PST>
+int pair_capacity_st(int sm_count) {
+  using Cfg = UmmaPairConfig<OP, PST, kPairKAtoms>;
+  static std::atomic<int> cached[kMaxDevices];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int fit = cached[dev].load(std::memory_order_acquire);
+  if (fit == 0) {
+    cudaFuncSetAttribute(umma_gemm_pair_kernel<OP, PST, kPairKAtoms>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         Cfg::SMEM_BYTES);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(sm_count / 2 * 2), 1, 1);
+    cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, umma_gemm_pair_kernel<OP, PST, kPairKAtoms>, &cfg) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = sm_count / 2;
+    }
+    fit = n < sm_count / 2 ? n : sm_count / 2;
+    cached[dev].store(fit, std::memory_order_release);
+  }
+  return fit;
+}
+inline int pair_capacity(int op, int sm_count) {
+  switch (op) {
+    case OP_F16: return pair_capacity_st<OP_F16, kPairStages>(sm_count);
+    case OP_BF16: return pair_capacity_st<OP_BF16, kPairStages>(sm_count);
+    case OP_TF32: return pair_capacity_st<OP_TF32, kPairStages>(sm_count);
+    default: return pair_capacity_st<OP_I8, kPairStages>(sm_count);
+  }
+}
+
 template <int OP, int PST>
 cudaError_t launch_pair_st(const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b0,
                           const CUtensorMap& b1, const UmmaGemmParams& p, int grid, cudaStream_t s) {
@@ -282,21 +330,6 @@ cudaError_t launch_pair_st(const CUtensorMap& a0, const CUtensorMap& a1, const C
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  // The tile walk assumes every launched pair is resident at once; the driver knows how many
-  // clusters of this shape fit (a GPC with an odd SM count leaves one SM without a partner).
-  static std::atomic<int> max_clusters[kMaxDevices];
-  int fit = max_clusters[dev].load(std::memory_order_acquire);
-  if (fit == 0) {
-    int n = 0;
-    cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
-    if (cudaOccupancyMaxActiveClusters(&n, umma_gemm_pair_kernel<OP, PST, kPairKAtoms>, &cfg) != cudaSuccess || n <= 0) {
-      cudaGetLastError();
-      n = grid / 2;
-    }
-    fit = n;
-    max_clusters[dev].store(fit, std::memory_order_release);
-  }
-  if (grid / 2 > fit) cfg.gridDim = dim3(static_cast<unsigned>(2 * fit), 1, 1);
   cudaError_t e = cudaLaunchKernelEx(&cfg, umma_gemm_pair_kernel<OP, PST, kPairKAtoms>, a0, a1, b0, b1, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return e != cudaSuccess ? e : cudaGetLastError();
@@ -331,7 +364,7 @@ cudaError_t launch_split(Context* c, const void* src, float* hi, float* lo, size
 }
 
 int ensure_workspace(Context* c, size_t bytes, cudaStream_t s) {
-  if (c->ws_used) {
+  if (c->ws_used && c->ws_stream != s) {
     // the previous user of the scratch may still be running on another stream
     TVB_CUDA(cudaStreamWaitEvent(s, c->ws_event, 0));
   }
@@ -423,6 +456,13 @@ int run_umma(Context* c, const UmmaPlan& plan, const void* A, const void* B, voi
     if (v >= 1 && v <= 4096) p.k_chunk_blocks = v;
   }
   p.total_tiles = static_cast<uint32_t>(batch * p.m_tiles * p.n_tiles);
+  p.split_from = p.total_tiles;
+  p.split_parts = 1;
+  p.split_kw = 0;
+  p.total_items = p.total_tiles;
+  p.epoch = 0;
+  p.partial = nullptr;
+  p.flags = c->d_flags;
   p.C = C;
   p.status = c->d_status;
   p.wait_limit_ns = static_cast<uint64_t>(g_wait_limit_ms.load()) * 1000000ull;
@@ -430,8 +470,37 @@ int run_umma(Context* c, const UmmaPlan& plan, const void* A, const void* B, voi
                                                                                        : c->sm_count);
   cudaError_t e;
   if (plan.pair) {
-    const uint32_t pairs = static_cast<uint32_t>(c->sm_count / 2);
-    const int pgrid = 2 * static_cast<int>(p.total_tiles < pairs ? p.total_tiles : pairs);
+    const uint32_t pairs = static_cast<uint32_t>(pair_capacity(plan.op, c->sm_count));
+    // An incomplete last wave of R tiles keeps R pairs busy for a whole tile time while the
+    // rest idle.  When at least 2R pairs exist, each of those tiles is shared by S = pairs/R
+    // pairs that take consecutive ranges of K; S-1 of them pass their raw sums through
+    // scratch memory to the tile's owner.  (Not for fp32: its epilogue already sums K chunks
+    // in registers, and its scratch is in use.)
+    const uint32_t rest = p.total_tiles % pairs;
+    if (plan.op != OP_TF32 && rest > 0 && 2 * rest <= pairs && getenv("TVB_NO_SPLIT_K") == nullptr) {
+      // Two shares per tile.  Handing a partial sum over costs about 4 us (measured: raw sums
+      // out through L2, fence, flag, sums in), part of which the non-owning share hides by
+      // taking fewer stages.  Against a tile time of 21 us at 32 stages the split gains 1.5 %,
+      // at 64 stages 3.7 %, at 128 stages 5 %; it is used from 64 stages on.
+      const uint32_t parts = 2;
+      const uint32_t kb = static_cast<uint32_t>(p.k_blocks);
+      const uint32_t shift = kb / 16;
+      const uint32_t kw = kb / 2 > shift ? kb / 2 - shift : 0;
+      const size_t slots = static_cast<size_t>(rest) * (parts - 1);
+      if (kb >= 64 && kw >= 1 && slots * 8 <= static_cast<size_t>(Context::kMaxFlags)) {
+        if (!lock.owns_lock()) lock.lock();
+        int rcw = ensure_workspace(c, slots * 2 * 128 * 256 * sizeof(uint32_t), s);
+        if (rcw != TVB_OK) return rcw;
+        p.split_from = p.total_tiles - rest;
+        p.split_parts = parts;
+        p.split_kw = kw;
+        p.total_items = p.split_from + rest * parts;
+        p.partial = static_cast<uint32_t*>(c->ws);
+        if (++c->sk_epoch == 0) ++c->sk_epoch;
+        p.epoch = c->sk_epoch;
+      }
+    }
+    const int pgrid = 2 * static_cast<int>(p.total_items < pairs ? p.total_items : pairs);
     switch (plan.op) {
       case OP_F16: e = launch_pair_t<OP_F16>(plan.stages, ma0, ma1, mb0, mb1, p, pgrid, s); break;
       case OP_BF16: e = launch_pair_t<OP_BF16>(plan.stages, ma0, ma1, mb0, mb1, p, pgrid, s); break;
@@ -446,9 +515,12 @@ int run_umma(Context* c, const UmmaPlan& plan, const void* A, const void* B, voi
     default: e = launch_umma_op<OP_I8>(plan.block_n, ma0, ma1, mb0, mb1, p, grid, s); break;
   }
   if (e != cudaSuccess) return fail(TVB_ERR_CUDA, "tcgen05 GEMM launch failed: %s", cudaGetErrorString(e));
-  if (plan.op == OP_TF32) {
+  if (plan.op == OP_TF32 || p.split_parts > 1) {
+    // a later user on ANOTHER stream waits for this event; users on the same stream are
+    // ordered already and skip the wait
     TVB_CUDA(cudaEventRecord(c->ws_event, s));
     c->ws_used = true;
+    c->ws_stream = s;
   }
   return TVB_OK;
 }
@@ -615,6 +687,8 @@ int tvb_init(int device) {
   TVB_CUDA(cudaEventCreateWithFlags(&c->ev_out, cudaEventDisableTiming));
   TVB_CUDA(cudaMalloc(&c->d_status, sizeof(uint32_t)));
   TVB_CUDA(cudaMemset(c->d_status, 0, sizeof(uint32_t)));
+  TVB_CUDA(cudaMalloc(&c->d_flags, Context::kMaxFlags * sizeof(uint32_t)));
+  TVB_CUDA(cudaMemset(c->d_flags, 0, Context::kMaxFlags * sizeof(uint32_t)));
   TVB_CUDA(cudaHostAlloc(&c->h_status, sizeof(uint32_t), cudaHostAllocDefault));
   *c->h_status = 0;
   c->pool = new BlockPool(backing_alloc, backing_free, c);
@@ -632,6 +706,7 @@ int tvb_shutdown(void) {
     if (c->ws) c->pool->release(c->ws);
     delete c->pool;
     cudaFree(c->d_status);
+    cudaFree(c->d_flags);
     cudaFreeHost(c->h_status);
     cudaEventDestroy(c->ws_event);
     for (auto& e : c->ev_in) cudaEventDestroy(e);

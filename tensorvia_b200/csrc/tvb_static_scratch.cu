@@ -211,6 +211,13 @@ extern "C" int tvb_matmul_f32_static(int device, const void* A, const void* B, v
   const int64_t tiles = batch * p.m_tiles * p.n_tiles;
   if (tiles > 0x7FFFFFFFll) return fail(TVB_ERR_SHAPE, "too many output tiles");
   p.total_tiles = static_cast<uint32_t>(tiles);
+  p.split_from = p.total_tiles;
+  p.split_parts = 1;
+  p.split_kw = 0;
+  p.total_items = p.total_tiles;
+  p.epoch = 0;
+  p.partial = nullptr;
+  p.flags = nullptr;
   p.C = C;
   p.status = d->status;
   p.wait_limit_ns = 2000000000ull;

@@ -83,6 +83,18 @@ struct UmmaGemmParams {
   int32_t passes;        // 1, or 3 when fp32 runs as (A_lo,B_hi), (A_hi,B_lo), (A_hi,B_hi)
   int32_t k_chunk_blocks;// stages of K summed inside TMEM before the sum moves to registers
   uint32_t total_tiles;  // batch * m_tiles * n_tiles
+  // CTA-pair kernel only.  Work items [0, split_from) are whole tiles.  The tiles of an
+  // incomplete last wave, [split_from, total_tiles), are each shared by `split_parts` pairs
+  // that take consecutive ranges of K: item split_from + j is part j % split_parts of tile
+  // split_from + j / split_parts.  Parts >= 1 write their raw accumulator to `partial` and
+  // then `epoch` to their flag; part 0 adds them to its own sum and writes C.
+  uint32_t split_from;
+  uint32_t split_parts;
+  uint32_t split_kw;     // stages of K of every share but the owner's
+  uint32_t total_items;
+  uint32_t epoch;
+  uint32_t* partial;     // [tile - split_from][part - 1][cta rank][64 column groups of 16 B][128 rows] of 32-bit sums
+  uint32_t* flags;       // [tile - split_from][part - 1][cta rank][row quarter]
   void* C;
   uint32_t* status;
   uint64_t wait_limit_ns;

@@ -44,6 +44,46 @@ struct UmmaPairConfig {
   static constexpr int THREADS = 64 + 32 * EPI_WARPS;
 };
 
+// One unit of work of a pair: a tile and the stages of K it covers.
+struct PairItem {
+  int b, mt, nt;
+  int kb_begin, kb_end;   // stages of K
+  uint32_t part, parts;   // parts > 1: the tile's K range is shared, this is share `part`
+  uint32_t slot;          // index of (tile, part) among the shared partial results (part >= 1)
+};
+
+__device__ __forceinline__ PairItem decode_item(uint32_t item, const UmmaGemmParams& p) {
+  PairItem w;
+  uint32_t tile = item;
+  w.kb_begin = 0;
+  w.kb_end = p.k_blocks;
+  w.part = 0;
+  w.parts = 1;
+  w.slot = 0;
+  if (item >= p.split_from) {
+    const uint32_t j = item - p.split_from;
+    const uint32_t t = j / p.split_parts;
+    tile = p.split_from + t;
+    w.part = j - t * p.split_parts;
+    w.parts = p.split_parts;
+    // Shares 1 .. parts-1 take `split_kw` stages each from the front of K; the owner (part 0)
+    // takes the rest, which is a little more: the others then finish early enough for their
+    // sums to be in memory when the owner's own sum is complete.
+    const int kw = static_cast<int>(p.split_kw);
+    if (w.part == 0) {
+      w.kb_begin = kw * static_cast<int>(p.split_parts - 1);
+      w.kb_end = p.k_blocks;
+    } else {
+      w.kb_begin = kw * static_cast<int>(w.part - 1);
+      w.kb_end = w.kb_begin + kw;
+    }
+    // part >= 1: its own slot; part 0 (the owner): the slot of part 1, the others follow it
+    w.slot = t * (p.split_parts - 1) + (w.part ? w.part - 1 : 0);
+  }
+  decode_tile(tile, p, w.b, w.mt, w.nt);
+  return w;
+}
+
 // p.m_tiles counts 256-row tiles here; everything else as in UmmaGemmParams.
 template <int OP, int STAGES, int KATOMS>
 __global__ void __launch_bounds__(64 + 32 * UmmaEpilogue<OP>::WARPS, 1)
@@ -130,12 +170,12 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_con
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (uint32_t tile = pair; ok && tile < p.total_tiles; tile += num_pairs) {
-        int b, mt, nt;
-        decode_tile(tile, p, b, mt, nt);
-        const int row0 = mt * Cfg::BLOCK_M + static_cast<int>(rank) * 128;
-        const int col0 = nt * BLOCK_N + static_cast<int>(rank) * HALF_B;
-        for (int kb = 0; ok && kb < p.k_blocks; ++kb) {
+      for (uint32_t item = pair; ok && item < p.total_items; item += num_pairs) {
+        const PairItem w = decode_item(item, p);
+        const int b = w.b;
+        const int row0 = w.mt * Cfg::BLOCK_M + static_cast<int>(rank) * 128;
+        const int col0 = w.nt * BLOCK_N + static_cast<int>(rank) * HALF_B;
+        for (int kb = w.kb_begin; ok && kb < w.kb_end; ++kb) {
           for (int pass = 0; pass < p.passes; ++pass) {
             if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, p.wait_limit_ns)) {
               atomicOr(p.status, ST_PRODUCER_TIMEOUT);
@@ -175,8 +215,12 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_con
       uint32_t phase = 0;
       uint32_t local = 0;
       bool ok = true;
-      for (uint32_t tile = pair; ok && tile < p.total_tiles; tile += num_pairs) {
-        for (int ch = 0; ok && ch < chunks; ++ch, ++local) {
+      for (uint32_t item = pair; ok && item < p.total_items; item += num_pairs) {
+        const PairItem w = decode_item(item, p);
+        // (the chunked fp32 path never shares a tile: its items always cover all of K)
+        const int kc_item = CHUNKED ? kc : (w.kb_end - w.kb_begin);
+        const int chunks_item = CHUNKED ? chunks : 1;
+        for (int ch = 0; ok && ch < chunks_item; ++ch, ++local) {
           const uint32_t buf = local & 1u;
           const uint32_t acc_phase = (local >> 1) & 1u;
           if (!ptx::mbar_wait(tempty_bar(buf), acc_phase ^ 1u, p.wait_limit_ns)) {
@@ -186,8 +230,8 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_con
           }
           ptx::tc_fence_after();
           const uint32_t d_tmem = tmem_base + buf * BLOCK_N;
-          const int kb_end = min(p.k_blocks, (ch + 1) * kc);
-          const int k_iters = (kb_end - ch * kc) * p.passes;
+          const int kb_end = min(w.kb_end, w.kb_begin + (ch + 1) * kc_item);
+          const int k_iters = (kb_end - (w.kb_begin + ch * kc_item)) * p.passes;
           for (int it = 0; it < k_iters; ++it) {
             if (!ptx::mbar_wait(full_bar(stage), phase, p.wait_limit_ns)) {
               atomicOr(p.status, ST_MMA_TIMEOUT);
@@ -222,9 +266,9 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_con
     bool ok = true;
     Out* const Cbase = reinterpret_cast<Out*>(p.C);
     if constexpr (!CHUNKED) {
-      for (uint32_t tile = pair; ok && tile < p.total_tiles; tile += num_pairs, ++local) {
-        int b, mt, nt;
-        decode_tile(tile, p, b, mt, nt);
+      for (uint32_t item = pair; ok && item < p.total_items; item += num_pairs, ++local) {
+        const PairItem w = decode_item(item, p);
+        const int b = w.b, mt = w.mt, nt = w.nt;
         const uint32_t buf = local & 1u;
         const uint32_t acc_phase = (local >> 1) & 1u;
         const bool landed = ptx::mbar_wait(tfull_bar(buf), acc_phase, p.wait_limit_ns);
@@ -238,16 +282,81 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_con
         const int col0 = nt * BLOCK_N;
         const uint32_t taddr = tmem_base + buf * BLOCK_N + (static_cast<uint32_t>(quad * 32) << 16);
         Out* crow = Cbase + (static_cast<size_t>(b) * p.M + static_cast<size_t>(row)) * p.N + col0;
+        // A shared partial result is laid out [slot][cta rank][16-byte group of columns][row], so
+        // that the 32 lanes of a warp (32 rows) touch 512 contiguous bytes per access.
+        auto partial_vec = [&](uint32_t slot, int group) {
+          return reinterpret_cast<uint4*>(p.partial) +
+                 ((static_cast<size_t>(slot) * 2 + rank) * (BLOCK_N / 4) + group) * 128 + quad * 32 + lane;
+        };
+        auto flag_of = [&](uint32_t slot) { return p.flags + (static_cast<size_t>(slot) * 2 + rank) * 4 + quad; };
+
+        if (w.part >= 1) {
+          // ---- a share of K that is not the tile's owner: hand the raw sums over
 #pragma unroll 1
-        for (int c = 0; c < BLOCK_N / 64; ++c) {
-          // two 32-column loads in flight per wait: half as many TMEM round trips
-          uint32_t v0[32], v1[32];
-          ptx::tmem_ld_32x32(taddr + c * 64, v0);
-          ptx::tmem_ld_32x32(taddr + c * 64 + 32, v1);
-          ptx::tmem_ld_wait();
-          const int cols_left = p.N - (col0 + c * 64);
-          if (row < p.M && cols_left > 0) store_row_chunk<OP>(crow + c * 64, v0, cols_left);
-          if (row < p.M && cols_left > 32) store_row_chunk<OP>(crow + c * 64 + 32, v1, cols_left - 32);
+          for (int c = 0; c < BLOCK_N / 64; ++c) {
+            uint32_t v0[32], v1[32];
+            ptx::tmem_ld_32x32(taddr + c * 64, v0);
+            ptx::tmem_ld_32x32(taddr + c * 64 + 32, v1);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int g = 0; g < 8; ++g)
+              *partial_vec(w.slot, c * 16 + g) = make_uint4(v0[4 * g], v0[4 * g + 1], v0[4 * g + 2], v0[4 * g + 3]);
+#pragma unroll
+            for (int g = 0; g < 8; ++g)
+              *partial_vec(w.slot, c * 16 + 8 + g) = make_uint4(v1[4 * g], v1[4 * g + 1], v1[4 * g + 2], v1[4 * g + 3]);
+          }
+          __threadfence();   // every lane's rows are visible device-wide ...
+          __syncwarp();
+          if (lane == 0) *reinterpret_cast<volatile uint32_t*>(flag_of(w.slot)) = p.epoch;  // ... before the flag is
+        } else {
+          if (w.parts > 1) {
+            // ---- the owner of a shared tile: wait (bounded) for the other shares' rows
+            bool there = true;
+            if (lane == 0) {
+              const uint32_t first = w.slot;  // slot of part 1 of this tile
+              for (uint32_t q = 0; q + 1 < w.parts && there; ++q) {
+                const volatile uint32_t* f = reinterpret_cast<const volatile uint32_t*>(flag_of(first + q));
+                const uint64_t t0 = ptx::globaltimer_ns();
+                while (*f != p.epoch) {
+                  if (ptx::globaltimer_ns() - t0 > p.wait_limit_ns) { there = false; break; }
+                  __nanosleep(200);
+                }
+              }
+              __threadfence();
+            }
+            there = __shfl_sync(0xffffffffu, there ? 1 : 0, 0) != 0;
+            if (!there) {
+              if (lane == 0) atomicOr(p.status, ST_EPILOGUE_TIMEOUT);
+              ok = false;
+              break;
+            }
+          }
+#pragma unroll 1
+          for (int c = 0; c < BLOCK_N / 64; ++c) {
+            // two 32-column loads in flight per wait: half as many TMEM round trips
+            uint32_t v0[32], v1[32];
+            ptx::tmem_ld_32x32(taddr + c * 64, v0);
+            ptx::tmem_ld_32x32(taddr + c * 64 + 32, v1);
+            ptx::tmem_ld_wait();
+            for (uint32_t q = 0; q + 1 < w.parts; ++q) {
+#pragma unroll
+              for (int g = 0; g < 16; ++g) {
+                const uint4 u = __ldcg(partial_vec(w.slot + q, c * 16 + g));
+                uint32_t* v = g < 8 ? &v0[4 * g] : &v1[4 * (g - 8)];
+                if constexpr (OP == OP_I8) {
+                  v[0] += u.x; v[1] += u.y; v[2] += u.z; v[3] += u.w;
+                } else {
+                  v[0] = __float_as_uint(__uint_as_float(v[0]) + __uint_as_float(u.x));
+                  v[1] = __float_as_uint(__uint_as_float(v[1]) + __uint_as_float(u.y));
+                  v[2] = __float_as_uint(__uint_as_float(v[2]) + __uint_as_float(u.z));
+                  v[3] = __float_as_uint(__uint_as_float(v[3]) + __uint_as_float(u.w));
+                }
+              }
+            }
+            const int cols_left = p.N - (col0 + c * 64);
+            if (row < p.M && cols_left > 0) store_row_chunk<OP>(crow + c * 64, v0, cols_left);
+            if (row < p.M && cols_left > 32) store_row_chunk<OP>(crow + c * 64 + 32, v1, cols_left - 32);
+          }
         }
         ptx::tc_fence_before();
         __syncwarp();
@@ -257,9 +366,9 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_con
       constexpr int HALF_N = BLOCK_N / 2;
       const int half = (warp - 2) >> 2;
       float acc[HALF_N];
-      for (uint32_t tile = pair; ok && tile < p.total_tiles; tile += num_pairs) {
-        int b, mt, nt;
-        decode_tile(tile, p, b, mt, nt);
+      for (uint32_t item = pair; ok && item < p.total_items; item += num_pairs) {
+        const PairItem w = decode_item(item, p);   // never a shared tile on this path
+        const int b = w.b, mt = w.mt, nt = w.nt;
 #pragma unroll
         for (int j = 0; j < HALF_N; ++j) acc[j] = 0.f;
         for (int ch = 0; ch < chunks; ++ch, ++local) {

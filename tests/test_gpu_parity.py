@@ -175,3 +175,27 @@ def test_int8_accumulator_beyond_int32(dev):
     assert (c_simt == want).all()
     c_tc, _ = dev.matmul(A, R.INT8, B, R.INT8, algo=TCGEN05)
     assert (c_tc == want).all(), "tensor-core s32 accumulator does not wrap modulo 2^32"
+
+
+def test_shared_tiles_of_an_incomplete_wave(dev, tv, monkeypatch):
+    """Long-K problems whose last wave of 256x256 tiles is less than half full: each of those
+    tiles is computed by two SM pairs over two ranges of K, one handing its raw sums to the
+    other through scratch memory.  int8 must stay bit-exact, bf16 within tolerance; a second
+    run must reproduce the first (the hand-over flags carry a per-launch epoch)."""
+    monkeypatch.setenv("TVB_CTA_PAIR", "1")   # these shapes are below the size that picks pairs by itself
+    A = R.fill((512, 16384), R.INT8, 31, 1); B = R.fill((16384, 512), R.INT8, 32, 1)
+    want = (A.astype(np.int32) @ B.astype(np.int32)).astype(np.int8)
+    for _ in range(2):
+        c, dtc = dev.matmul(A, R.INT8, B, R.INT8, algo=TCGEN05)
+        assert dtc == R.INT8 and (c == want).all()
+    A = R.fill((2, 300, 8192), R.BFLOAT16, 33); B = R.fill((2, 8192, 520), R.BFLOAT16, 34)
+    exp, dte = R.oracle_matmul(A, R.BFLOAT16, B, R.BFLOAT16, "cuda")
+    c1, dtc = dev.matmul(A, R.BFLOAT16, B, R.BFLOAT16, algo=TCGEN05)
+    assert_matches(c1, dtc, exp, dte, what="bf16 shared tiles")
+    c2, _ = dev.matmul(A, R.BFLOAT16, B, R.BFLOAT16, algo=TCGEN05)
+    assert c1.tobytes() == c2.tobytes()
+    monkeypatch.setenv("TVB_NO_SPLIT_K", "1")
+    c3, _ = dev.matmul(A, R.BFLOAT16, B, R.BFLOAT16, algo=TCGEN05)
+    assert_matches(c3, dtc, exp, dte, what="bf16 whole tiles")
+    # the two schedules add the same products in a different order: equal to fp32 rounding
+    assert R.rel_frobenius(c1, c3, R.BFLOAT16) < 1e-3
