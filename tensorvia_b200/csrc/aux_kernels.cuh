@@ -44,15 +44,54 @@ split_tf32_kernel(const float4* __restrict__ x, float4* __restrict__ hi, float4*
   }
 }
 
+// The split for operands whose rows do not start on 16-byte boundaries (K not a multiple of 4,
+// or an unaligned base): one element per thread, destination rows padded to `kp` floats so that
+// TMA can address them.  src is [rows][k] dense, hi/lo are [rows][kp].
+static __global__ void __launch_bounds__(256)
+split_tf32_rows_kernel(const float* __restrict__ src, float* __restrict__ hi, float* __restrict__ lo,
+                       size_t rows, int k, int kp) {
+  const size_t total = rows * static_cast<size_t>(k);
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const size_t r = i / k;
+    const int c = static_cast<int>(i - r * k);
+    const float v = src[i];
+    const float h = round_tf32(v);
+    hi[r * kp + c] = h;
+    lo[r * kp + c] = round_tf32(v - h);
+  }
+}
+
+// Copies dense rows of `width` bytes into rows of `dpitch` bytes (dpitch a multiple of 16, the
+// tail of each row zero-filled): gives 1- and 2-byte operands with an odd row length, or an
+// unaligned base, the 16-byte row pitch TMA needs.  One thread per 16 bytes of destination.
+static __global__ void __launch_bounds__(256)
+pad_rows_kernel(const unsigned char* __restrict__ src, unsigned char* __restrict__ dst, size_t rows,
+                size_t width, size_t dpitch) {
+  const size_t vec_per_row = dpitch / 16;
+  const size_t total = rows * vec_per_row;
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const size_t r = i / vec_per_row;
+    const size_t x = (i - r * vec_per_row) * 16;
+    const unsigned char* s = src + r * width + x;
+    unsigned char b[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) b[j] = (x + j < width) ? s[j] : static_cast<unsigned char>(0);
+    *reinterpret_cast<uint4*>(dst + r * dpitch + x) = *reinterpret_cast<const uint4*>(b);
+  }
+}
+
 // Same split for the B operand, written transposed: src is [batch][K][N], hi and lo are
-// [batch][N][K], so the tensor core can read B K-major.  32x32 tiles go through shared
+// [batch][N][kp] (kp >= K, rows padded to 16 bytes), so the tensor core can read B K-major.  32x32 tiles go through shared
 // memory: reads are coalesced along N, writes along K.  grid = (ceil(N/32), ceil(K/32), batch).
 static __global__ void __launch_bounds__(256)
 split_tf32_transpose_kernel(const float* __restrict__ src, float* __restrict__ hi,
-                            float* __restrict__ lo, int K, int N) {
+                            float* __restrict__ lo, int K, int N, int kp) {
   __shared__ float th[32][33];
   __shared__ float tl[32][33];
   const size_t boff = static_cast<size_t>(blockIdx.z) * K * N;
+  const size_t ooff = static_cast<size_t>(blockIdx.z) * N * kp;
   const int n0 = blockIdx.x * 32, k0 = blockIdx.y * 32;
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
 #pragma unroll
@@ -72,7 +111,7 @@ split_tf32_transpose_kernel(const float* __restrict__ src, float* __restrict__ h
   for (int j = 0; j < 4; ++j) {
     const int n = n0 + ty + 8 * j, k = k0 + tx;
     if (n < N && k < K) {
-      const size_t o = boff + static_cast<size_t>(n) * K + k;
+      const size_t o = ooff + static_cast<size_t>(n) * kp + k;
       hi[o] = th[tx][ty + 8 * j];
       lo[o] = tl[tx][ty + 8 * j];
     }

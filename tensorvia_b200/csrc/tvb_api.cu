@@ -133,12 +133,13 @@ size_t dtype_size(int d) {
 // ------------------------------------------------------------------------------------
 // tensor maps
 // ------------------------------------------------------------------------------------
-// 3-D map over a dense [batch, rows, cols] array (cols contiguous) with a
+// 3-D map over a [batch, rows, cols] array (cols contiguous, rows `pitch` elements apart) with a
 // [1, box_rows, box_cols] box, 128-byte swizzle and zero fill outside the array.
 int make_map(CUtensorMap* map, CUtensorMapDataType type, size_t es, const void* base, uint64_t cols,
-             uint64_t rows, uint64_t batch, uint32_t box_cols, uint32_t box_rows) {
+             uint64_t rows, uint64_t batch, uint64_t pitch, uint32_t box_cols, uint32_t box_rows) {
+  // `pitch` = elements from one row to the next (>= cols; pitch * es a multiple of 16)
   cuuint64_t dims[3] = {cols, rows, batch};
-  cuuint64_t strides[2] = {cols * es, rows * cols * es};
+  cuuint64_t strides[2] = {pitch * es, rows * pitch * es};
   cuuint32_t box[3] = {box_cols, box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = g_encode(map, type, 3, const_cast<void*>(base), dims, strides, box, estr,
@@ -199,8 +200,7 @@ struct UmmaPlan {
   CUtensorMapDataType tm_type = CU_TENSOR_MAP_DATA_TYPE_UINT8;
 };
 
-// Problems the tensor-core kernel takes: same-dtype f16 / bf16 / int8 / fp32 whose row
-// pitches (K and N elements) are whole multiples of 16 bytes (a TMA requirement).
+// Problems the tensor-core kernels take: same-dtype f16 / bf16 / int8 / fp32 of any shape.
 bool umma_eligible(int dta, int dtb, int64_t batch, int64_t M, int64_t K, int64_t N, const void* A,
                    const void* B, const void* C, UmmaPlan* plan) {
   if (dta != dtb) return false;
@@ -215,11 +215,11 @@ bool umma_eligible(int dta, int dtb, int64_t batch, int64_t M, int64_t K, int64_
       break;
     default: return false;
   }
-  if ((K * p.es) % 16 != 0 || (N * p.es) % 16 != 0) return false;
+  // Row pitches that are not multiples of 16 bytes and unaligned bases are fine: such operands
+  // are first copied into padded scratch rows (fp32 passes through a split pass anyway).
+  (void)A; (void)B; (void)C;
   if (p.op == OP_TF32 && (K + 31) / 32 > 65535) return false;  // grid.y of the transposing split
   if (M > 0x7FFFFFFFll || N > 0x7FFFFFFFll || K > 0x7FFFFFFFll || batch > 0x7FFFFFFFll) return false;
-  auto mis = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) != 0; };
-  if ((A && mis(A)) || (B && mis(B)) || (C && mis(C))) return false;
   // Narrow outputs use 128-column tiles (less padding); everything else 256.
   p.block_n = (N <= 128) ? 128 : 256;
   if (const char* e = getenv("TVB_BLOCK_N")) {
@@ -394,14 +394,50 @@ int run_umma(Context* c, const UmmaPlan& plan, const void* A, const void* B, voi
   const void* b_hi = B;
   const void* a_lo = A;
   const void* b_lo = B;
+  auto misaligned = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) != 0; };
+  auto round_up = [](size_t v, size_t m) { return (v + m - 1) / m * m; };
+  const size_t vec = 16 / es;                                   // elements per 16 bytes
+  uint64_t pitch_a = static_cast<uint64_t>(K);                  // elements between rows of A as the kernel sees it
+  uint64_t pitch_b = static_cast<uint64_t>(N);                  // ... of B ([K,N]; for fp32: of B^T, [N,K])
+  const bool c_vec = (N * es) % 16 == 0 && !misaligned(C);
+
+  // Shared-tile plan of the pair kernel (decided here because its scratch shares the block)
+  uint32_t sk_rest = 0, sk_kw = 0;
+  uint32_t pairs = 0;
+  const int32_t k_blocks = static_cast<int32_t>((K + bk - 1) / bk);
+  const uint32_t total_tiles = static_cast<uint32_t>(batch * ((M + plan.tile_m - 1) / plan.tile_m) *
+                                                     ((N + plan.block_n - 1) / plan.block_n));
+  if (plan.pair) {
+    pairs = static_cast<uint32_t>(pair_capacity(plan.op, c->sm_count));
+    // An incomplete last wave of R tiles keeps R pairs busy for a whole tile time while the
+    // rest idle.  When at least 2R pairs exist and K is long, each of those tiles is shared by
+    // two pairs that take consecutive ranges of K; one passes its raw sums through scratch
+    // memory to the tile's owner.  Handing a sum over costs about 4 us (measured: raw sums out
+    // through L2, fence, flag, sums in), part of which the non-owning share hides by taking
+    // fewer stages.  Against a tile time of 21 us at 32 stages the split gains 1.5 %, at 64
+    // stages 3.7 %, at 128 stages 5 %; it is used from 64 stages on.  (Not for fp32: its
+    // epilogue already sums K chunks in registers.)
+    const uint32_t rest = total_tiles % pairs;
+    const uint32_t kb = static_cast<uint32_t>(k_blocks);
+    const uint32_t shift = kb / 16;
+    const uint32_t kw = kb / 2 > shift ? kb / 2 - shift : 0;
+    if (plan.op != OP_TF32 && rest > 0 && 2 * rest <= pairs && kb >= 64 && kw >= 1 &&
+        static_cast<size_t>(rest) * 8 <= static_cast<size_t>(Context::kMaxFlags) &&
+        getenv("TVB_NO_SPLIT_K") == nullptr) {
+      sk_rest = rest;
+      sk_kw = kw;
+    }
+  }
+  const size_t partial_bytes = static_cast<size_t>(sk_rest) * 2 * 128 * 256 * sizeof(uint32_t);
 
   std::unique_lock<std::mutex> lock(c->mu, std::defer_lock);
   if (plan.op == OP_TF32) {
-    // fp32: split both operands into TF32 hi and lo parts in scratch memory
-    // (B transposed on the way); the 1xTF32 mode uses the hi parts only
+    // fp32: split both operands into TF32 hi and lo parts in scratch memory (B transposed on
+    // the way, rows padded to 16 bytes); the 1xTF32 mode uses the hi parts only
     lock.lock();
-    const size_t na = static_cast<size_t>(batch) * M * K, nb = static_cast<size_t>(batch) * K * N;
-    const size_t na_b = (na * 4 + 255) / 256 * 256, nb_b = (nb * 4 + 255) / 256 * 256;
+    const size_t kp = round_up(static_cast<size_t>(K), 4);
+    const size_t na = static_cast<size_t>(batch) * M * kp, nb = static_cast<size_t>(batch) * N * kp;
+    const size_t na_b = round_up(na * 4, 256), nb_b = round_up(nb * 4, 256);
     int rc = ensure_workspace(c, 2 * na_b + 2 * nb_b, s);
     if (rc != TVB_OK) return rc;
     char* w = static_cast<char*>(c->ws);
@@ -409,35 +445,81 @@ int run_umma(Context* c, const UmmaPlan& plan, const void* A, const void* B, voi
     float* alo = reinterpret_cast<float*>(w + na_b);
     float* bhi = reinterpret_cast<float*>(w + 2 * na_b);
     float* blo = reinterpret_cast<float*>(w + 2 * na_b + nb_b);
-    TVB_CUDA(launch_split(c, A, ahi, alo, na, s));
-    {
-      // B is split and transposed to [batch][N][K] in the same pass
-      for (int64_t b0 = 0; b0 < batch; b0 += 65535) {
-        const int nbz = static_cast<int>(batch - b0 < 65535 ? batch - b0 : 65535);
-        dim3 grid(static_cast<unsigned>((N + 31) / 32), static_cast<unsigned>((K + 31) / 32), nbz);
-        const size_t off = static_cast<size_t>(b0) * K * N;
-        split_tf32_transpose_kernel<<<grid, 256, 0, s>>>(static_cast<const float*>(B) + off, bhi + off,
-                                                          blo + off, static_cast<int>(K),
-                                                          static_cast<int>(N));
-        g_launches.fetch_add(1, std::memory_order_relaxed);
-        TVB_CUDA(cudaGetLastError());
-      }
+    if (kp == static_cast<size_t>(K) && !misaligned(A)) {
+      TVB_CUDA(launch_split(c, A, ahi, alo, na, s));
+    } else {
+      const size_t rows = static_cast<size_t>(batch) * M;
+      size_t blocks = (rows * K + 255) / 256;
+      const size_t cap = static_cast<size_t>(c->sm_count) * 16;
+      if (blocks > cap) blocks = cap;
+      split_tf32_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+          static_cast<const float*>(A), ahi, alo, rows, static_cast<int>(K), static_cast<int>(kp));
+      g_launches.fetch_add(1, std::memory_order_relaxed);
+      TVB_CUDA(cudaGetLastError());
+    }
+    // B is split and transposed to [batch][N][kp] in the same pass
+    for (int64_t b0 = 0; b0 < batch; b0 += 65535) {
+      const int nbz = static_cast<int>(batch - b0 < 65535 ? batch - b0 : 65535);
+      dim3 grid(static_cast<unsigned>((N + 31) / 32), static_cast<unsigned>((K + 31) / 32), nbz);
+      split_tf32_transpose_kernel<<<grid, 256, 0, s>>>(
+          static_cast<const float*>(B) + static_cast<size_t>(b0) * K * N, bhi + static_cast<size_t>(b0) * N * kp,
+          blo + static_cast<size_t>(b0) * N * kp, static_cast<int>(K), static_cast<int>(N), static_cast<int>(kp));
+      g_launches.fetch_add(1, std::memory_order_relaxed);
+      TVB_CUDA(cudaGetLastError());
     }
     a_hi = ahi; a_lo = alo; b_hi = bhi; b_lo = blo;
+    pitch_a = kp;
+    pitch_b = kp;
+  } else {
+    // 1- and 2-byte operands are used in place when their rows start on 16-byte boundaries;
+    // otherwise they are copied once into padded rows
+    const bool pad_a = (K * es) % 16 != 0 || misaligned(A);
+    const bool pad_b = (N * es) % 16 != 0 || misaligned(B);
+    const size_t kpa = round_up(static_cast<size_t>(K), vec), npb = round_up(static_cast<size_t>(N), vec);
+    const size_t pa_bytes = pad_a ? round_up(static_cast<size_t>(batch) * M * kpa * es, 256) : 0;
+    const size_t pb_bytes = pad_b ? round_up(static_cast<size_t>(batch) * K * npb * es, 256) : 0;
+    if (partial_bytes + pa_bytes + pb_bytes > 0) {
+      lock.lock();
+      int rc = ensure_workspace(c, partial_bytes + pa_bytes + pb_bytes, s);
+      if (rc != TVB_OK) return rc;
+    }
+    char* w = static_cast<char*>(c->ws);
+    auto pad = [&](const void* src, void* dst, size_t rows, size_t width, size_t dpitch) -> cudaError_t {
+      size_t blocks = (rows * (dpitch / 16) + 255) / 256;
+      const size_t cap = static_cast<size_t>(c->sm_count) * 16;
+      if (blocks > cap) blocks = cap;
+      if (blocks == 0) blocks = 1;
+      pad_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(static_cast<const unsigned char*>(src),
+                                                                   static_cast<unsigned char*>(dst), rows, width, dpitch);
+      g_launches.fetch_add(1, std::memory_order_relaxed);
+      return cudaGetLastError();
+    };
+    if (pad_a) {
+      void* dst = w + partial_bytes;
+      TVB_CUDA(pad(A, dst, static_cast<size_t>(batch) * M, static_cast<size_t>(K) * es, kpa * es));
+      a_hi = a_lo = dst;
+      pitch_a = kpa;
+    }
+    if (pad_b) {
+      void* dst = w + partial_bytes + pa_bytes;
+      TVB_CUDA(pad(B, dst, static_cast<size_t>(batch) * K, static_cast<size_t>(N) * es, npb * es));
+      b_hi = b_lo = dst;
+      pitch_b = npb;
+    }
   }
 
   CUtensorMap ma0, ma1, mb0, mb1;
   int rc;
-  if ((rc = make_map(&ma0, plan.tm_type, es, a_hi, K, M, batch, atom_k, 128)) != TVB_OK) return rc;
-  if ((rc = make_map(&ma1, plan.tm_type, es, a_lo, K, M, batch, atom_k, 128)) != TVB_OK) return rc;
+  if ((rc = make_map(&ma0, plan.tm_type, es, a_hi, K, M, batch, pitch_a, atom_k, 128)) != TVB_OK) return rc;
+  if ((rc = make_map(&ma1, plan.tm_type, es, a_lo, K, M, batch, pitch_a, atom_k, 128)) != TVB_OK) return rc;
   if (plan.op == OP_TF32) {
     // B^T[batch][N][K]: boxes of block_n rows x 128 B of K
     const uint32_t b_rows = plan.pair ? 128u : static_cast<uint32_t>(plan.block_n);  // a pair loads half each
-    if ((rc = make_map(&mb0, plan.tm_type, es, b_hi, K, N, batch, atom_k, b_rows)) != TVB_OK) return rc;
-    if ((rc = make_map(&mb1, plan.tm_type, es, b_lo, K, N, batch, atom_k, b_rows)) != TVB_OK) return rc;
+    if ((rc = make_map(&mb0, plan.tm_type, es, b_hi, K, N, batch, pitch_b, atom_k, b_rows)) != TVB_OK) return rc;
+    if ((rc = make_map(&mb1, plan.tm_type, es, b_lo, K, N, batch, pitch_b, atom_k, b_rows)) != TVB_OK) return rc;
   } else {
-    if ((rc = make_map(&mb0, plan.tm_type, es, b_hi, N, K, batch, chunk_n, bk)) != TVB_OK) return rc;
-    if ((rc = make_map(&mb1, plan.tm_type, es, b_lo, N, K, batch, chunk_n, bk)) != TVB_OK) return rc;
+    if ((rc = make_map(&mb0, plan.tm_type, es, b_hi, N, K, batch, pitch_b, chunk_n, bk)) != TVB_OK) return rc;
+    if ((rc = make_map(&mb1, plan.tm_type, es, b_lo, N, K, batch, pitch_b, chunk_n, bk)) != TVB_OK) return rc;
   }
 
   UmmaGemmParams p;
@@ -464,41 +546,21 @@ int run_umma(Context* c, const UmmaPlan& plan, const void* A, const void* B, voi
   p.partial = nullptr;
   p.flags = c->d_flags;
   p.C = C;
+  p.c_vec = c_vec ? 1 : 0;
   p.status = c->d_status;
   p.wait_limit_ns = static_cast<uint64_t>(g_wait_limit_ms.load()) * 1000000ull;
   const int grid = static_cast<int>(p.total_tiles < static_cast<uint32_t>(c->sm_count) ? p.total_tiles
                                                                                        : c->sm_count);
   cudaError_t e;
   if (plan.pair) {
-    const uint32_t pairs = static_cast<uint32_t>(pair_capacity(plan.op, c->sm_count));
-    // An incomplete last wave of R tiles keeps R pairs busy for a whole tile time while the
-    // rest idle.  When at least 2R pairs exist, each of those tiles is shared by S = pairs/R
-    // pairs that take consecutive ranges of K; S-1 of them pass their raw sums through
-    // scratch memory to the tile's owner.  (Not for fp32: its epilogue already sums K chunks
-    // in registers, and its scratch is in use.)
-    const uint32_t rest = p.total_tiles % pairs;
-    if (plan.op != OP_TF32 && rest > 0 && 2 * rest <= pairs && getenv("TVB_NO_SPLIT_K") == nullptr) {
-      // Two shares per tile.  Handing a partial sum over costs about 4 us (measured: raw sums
-      // out through L2, fence, flag, sums in), part of which the non-owning share hides by
-      // taking fewer stages.  Against a tile time of 21 us at 32 stages the split gains 1.5 %,
-      // at 64 stages 3.7 %, at 128 stages 5 %; it is used from 64 stages on.
-      const uint32_t parts = 2;
-      const uint32_t kb = static_cast<uint32_t>(p.k_blocks);
-      const uint32_t shift = kb / 16;
-      const uint32_t kw = kb / 2 > shift ? kb / 2 - shift : 0;
-      const size_t slots = static_cast<size_t>(rest) * (parts - 1);
-      if (kb >= 64 && kw >= 1 && slots * 8 <= static_cast<size_t>(Context::kMaxFlags)) {
-        if (!lock.owns_lock()) lock.lock();
-        int rcw = ensure_workspace(c, slots * 2 * 128 * 256 * sizeof(uint32_t), s);
-        if (rcw != TVB_OK) return rcw;
-        p.split_from = p.total_tiles - rest;
-        p.split_parts = parts;
-        p.split_kw = kw;
-        p.total_items = p.split_from + rest * parts;
-        p.partial = static_cast<uint32_t*>(c->ws);
-        if (++c->sk_epoch == 0) ++c->sk_epoch;
-        p.epoch = c->sk_epoch;
-      }
+    if (sk_rest > 0) {
+      p.split_from = p.total_tiles - sk_rest;
+      p.split_parts = 2;
+      p.split_kw = sk_kw;
+      p.total_items = p.split_from + sk_rest * 2;
+      p.partial = static_cast<uint32_t*>(c->ws);   // the front of the scratch block
+      if (++c->sk_epoch == 0) ++c->sk_epoch;
+      p.epoch = c->sk_epoch;
     }
     const int pgrid = 2 * static_cast<int>(p.total_items < pairs ? p.total_items : pairs);
     switch (plan.op) {
@@ -515,7 +577,7 @@ int run_umma(Context* c, const UmmaPlan& plan, const void* A, const void* B, voi
     default: e = launch_umma_op<OP_I8>(plan.block_n, ma0, ma1, mb0, mb1, p, grid, s); break;
   }
   if (e != cudaSuccess) return fail(TVB_ERR_CUDA, "tcgen05 GEMM launch failed: %s", cudaGetErrorString(e));
-  if (plan.op == OP_TF32 || p.split_parts > 1) {
+  if (lock.owns_lock()) {   // this call used the scratch block
     // a later user on ANOTHER stream waits for this event; users on the same stream are
     // ordered already and skip the wait
     TVB_CUDA(cudaEventRecord(c->ws_event, s));
@@ -557,8 +619,7 @@ int matmul_impl(int device, const void* A, const void* B, void* C, int dta, int 
   const bool can_umma = umma_eligible(dta, dtb, batch, M, K, N, A, B, C, &plan);
   if (algo == TVB_ALGO_TCGEN05 && !can_umma)
     return fail(TVB_ERR_UNSUPPORTED,
-                "tcgen05 path needs same-dtype f16/bf16/int8/fp32 operands, 16-byte aligned pointers "
-                "and K, N row pitches that are multiples of 16 bytes");
+                "the tcgen05 path takes f16 x f16, bf16 x bf16, int8 x int8 and fp32 x fp32 only");
   if (can_umma && algo != TVB_ALGO_SIMT) {
     rc = run_umma(c, plan, A, B, C, batch, M, K, N, s);
     if (rc == TVB_OK || algo == TVB_ALGO_TCGEN05 || rc != TVB_ERR_UNSUPPORTED) return rc;
@@ -879,7 +940,8 @@ int tvb_matmul_plan(int device, int dta, int dtb, int64_t batch, int64_t M, int6
       out->ctas = static_cast<int>(out->tiles < static_cast<uint64_t>(c->sm_count) ? out->tiles : c->sm_count);
     }
     if (plan.op == OP_TF32) {
-      const size_t na = static_cast<size_t>(batch) * M * K, nb = static_cast<size_t>(batch) * K * N;
+      const size_t kp = (static_cast<size_t>(K) + 3) / 4 * 4;
+      const size_t na = static_cast<size_t>(batch) * M * kp, nb = static_cast<size_t>(batch) * N * kp;
       out->workspace_bytes = 2 * ((na * 4 + 255) / 256 * 256) + 2 * ((nb * 4 + 255) / 256 * 256);
     }
   } else {

@@ -187,7 +187,7 @@ extern "C" int tvb_matmul_f32_static(int device, const void* A, const void* B, v
     dim3 grid(static_cast<unsigned>((N + 31) / 32), static_cast<unsigned>((K + 31) / 32),
               static_cast<unsigned>(batch));
     split_tf32_transpose_kernel<<<grid, 256, 0, s>>>(static_cast<const float*>(B), bhi, blo,
-                                                     static_cast<int>(K), static_cast<int>(N));
+                                                     static_cast<int>(K), static_cast<int>(N), static_cast<int>(K));
     TVS_CUDA(cudaGetLastError());
   }
 
@@ -207,6 +207,7 @@ extern "C" int tvb_matmul_f32_static(int device, const void* A, const void* B, v
   p.n_tiles = static_cast<int32_t>((N + block_n - 1) / block_n);
   p.k_blocks = static_cast<int32_t>((K + 31) / 32);
   p.passes = 3;
+  p.c_vec = 1;
   p.k_chunk_blocks = 8;
   const int64_t tiles = batch * p.m_tiles * p.n_tiles;
   if (tiles > 0x7FFFFFFFll) return fail(TVB_ERR_SHAPE, "too many output tiles");

@@ -96,6 +96,7 @@ struct UmmaGemmParams {
   uint32_t* partial;     // [tile - split_from][part - 1][cta rank][64 column groups of 16 B][128 rows] of 32-bit sums
   uint32_t* flags;       // [tile - split_from][part - 1][cta rank][row quarter]
   void* C;
+  int32_t c_vec;         // rows of C start on 16-byte boundaries: 16-byte stores, else element stores
   uint32_t* status;
   uint64_t wait_limit_ns;
 };
@@ -194,6 +195,28 @@ __device__ __forceinline__ void store_row_chunk(typename OpTraits<OP>::Out* dst,
         d4[g] = make_uint4(w[0], w[1], w[2], w[3]);
       }
   }
+}
+
+// The same for a C whose rows are not 16-byte aligned (N odd, or an unaligned base): one
+// element per store.
+template <int OP>
+__device__ __forceinline__ void store_row_chunk_any(typename OpTraits<OP>::Out* dst, const uint32_t (&v)[32],
+                                                    int cols_left) {
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    if (j < cols_left) {
+      if constexpr (OP == OP_TF32) dst[j] = __uint_as_float(v[j]);
+      else if constexpr (OP == OP_F16) dst[j] = __float2half_rn(__uint_as_float(v[j]));
+      else if constexpr (OP == OP_BF16) dst[j] = __float2bfloat16_rn(__uint_as_float(v[j]));
+      else dst[j] = static_cast<int8_t>(v[j] & 0xFFu);
+    }
+  }
+}
+template <int OP>
+__device__ __forceinline__ void store_row_chunk_sel(typename OpTraits<OP>::Out* dst, const uint32_t (&v)[32],
+                                                    int cols_left, bool vec) {
+  if (vec) store_row_chunk<OP>(dst, v, cols_left);
+  else store_row_chunk_any<OP>(dst, v, cols_left);
 }
 
 template <int OP, int BLOCK_N, int STAGES>
@@ -385,8 +408,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
           ptx::tmem_ld_32x32(taddr + c * 64 + 32, v1);
           ptx::tmem_ld_wait();
           const int cols_left = p.N - (col0 + c * 64);
-          if (row < p.M && cols_left > 0) store_row_chunk<OP>(crow + c * 64, v0, cols_left);
-          if (row < p.M && cols_left > 32) store_row_chunk<OP>(crow + c * 64 + 32, v1, cols_left - 32);
+          if (row < p.M && cols_left > 0) store_row_chunk_sel<OP>(crow + c * 64, v0, cols_left, p.c_vec != 0);
+          if (row < p.M && cols_left > 32) store_row_chunk_sel<OP>(crow + c * 64 + 32, v1, cols_left - 32, p.c_vec != 0);
         }
         ptx::tc_fence_before();
         ptx::mbar_arrive(tempty_bar(buf));
@@ -429,13 +452,19 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
         const int row = mt * BLOCK_M + quad * 32 + lane;
         const int col0 = nt * BLOCK_N + half * HALF_N;
         if (row < p.M) {
-          float4* crow = reinterpret_cast<float4*>(
-              reinterpret_cast<float*>(Cbase) +
-              (static_cast<size_t>(b) * p.M + static_cast<size_t>(row)) * p.N + col0);
+          float* cf = reinterpret_cast<float*>(Cbase) +
+                      (static_cast<size_t>(b) * p.M + static_cast<size_t>(row)) * p.N + col0;
+          if (p.c_vec != 0) {
+            float4* crow = reinterpret_cast<float4*>(cf);
 #pragma unroll
-          for (int g = 0; g < HALF_N / 4; ++g)
-            if (col0 + g * 4 < p.N)
-              crow[g] = make_float4(acc[4 * g], acc[4 * g + 1], acc[4 * g + 2], acc[4 * g + 3]);
+            for (int g = 0; g < HALF_N / 4; ++g)
+              if (col0 + g * 4 < p.N)
+                crow[g] = make_float4(acc[4 * g], acc[4 * g + 1], acc[4 * g + 2], acc[4 * g + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < HALF_N; ++j)
+              if (col0 + j < p.N) cf[j] = acc[j];
+          }
         }
       }
     }

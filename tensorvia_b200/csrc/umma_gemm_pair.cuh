@@ -354,8 +354,8 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_con
               }
             }
             const int cols_left = p.N - (col0 + c * 64);
-            if (row < p.M && cols_left > 0) store_row_chunk<OP>(crow + c * 64, v0, cols_left);
-            if (row < p.M && cols_left > 32) store_row_chunk<OP>(crow + c * 64 + 32, v1, cols_left - 32);
+            if (row < p.M && cols_left > 0) store_row_chunk_sel<OP>(crow + c * 64, v0, cols_left, p.c_vec != 0);
+            if (row < p.M && cols_left > 32) store_row_chunk_sel<OP>(crow + c * 64 + 32, v1, cols_left - 32, p.c_vec != 0);
           }
         }
         ptx::tc_fence_before();
@@ -399,13 +399,19 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_con
         const int row = mt * Cfg::BLOCK_M + static_cast<int>(rank) * 128 + quad * 32 + lane;
         const int col0 = nt * BLOCK_N + half * HALF_N;
         if (row < p.M) {
-          float4* crow = reinterpret_cast<float4*>(
-              reinterpret_cast<float*>(Cbase) +
-              (static_cast<size_t>(b) * p.M + static_cast<size_t>(row)) * p.N + col0);
+          float* cf = reinterpret_cast<float*>(Cbase) +
+                      (static_cast<size_t>(b) * p.M + static_cast<size_t>(row)) * p.N + col0;
+          if (p.c_vec != 0) {
+            float4* crow = reinterpret_cast<float4*>(cf);
 #pragma unroll
-          for (int g = 0; g < HALF_N / 4; ++g)
-            if (col0 + g * 4 < p.N)
-              crow[g] = make_float4(acc[4 * g], acc[4 * g + 1], acc[4 * g + 2], acc[4 * g + 3]);
+            for (int g = 0; g < HALF_N / 4; ++g)
+              if (col0 + g * 4 < p.N)
+                crow[g] = make_float4(acc[4 * g], acc[4 * g + 1], acc[4 * g + 2], acc[4 * g + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < HALF_N; ++j)
+              if (col0 + j < p.N) cf[j] = acc[j];
+          }
         }
       }
     }

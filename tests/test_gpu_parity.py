@@ -107,19 +107,48 @@ def test_tcgen05_and_simt_agree(dev, dt):
         assert_matches(c1, d1, c2, d2, what="tcgen05 vs simt")
 
 
-def test_auto_falls_back_when_pitch_is_not_16_bytes(dev, tv):
-    # K = 30 halves = 60 bytes per row: TMA cannot address it; AUTO uses the CUDA-core kernel
-    A = R.fill((50, 30), R.BFLOAT16, 1); B = R.fill((30, 44), R.BFLOAT16, 2)
-    info = tv.ops.plan(R.BFLOAT16, R.BFLOAT16, 1, 50, 30, 44)
+@pytest.mark.parametrize("dt", TC_DTYPES)
+def test_tensor_cores_take_any_pitch_and_alignment(dev, tv, dt):
+    """K or N whose rows are not multiples of 16 bytes, and buffers that do not start on a
+    16-byte boundary: the operands go through padded scratch rows and C is written element by
+    element; the result is the same as for any other shape."""
+    for i, (batch, M, K, N) in enumerate([(1, 50, 30, 44), (1, 300, 77, 93), (2, 129, 255, 257), (1, 1, 1, 1),
+                                          (1, 513, 1001, 250), (3, 64, 7, 515)]):
+        sa = (batch, M, K) if batch > 1 else (M, K)
+        sb = (batch, K, N) if batch > 1 else (K, N)
+        A = R.fill(sa, dt, 700 + i, F(dt)); B = R.fill(sb, dt, 800 + i, F(dt))
+        info = tv.ops.plan(dt, dt, batch, M, K, N)
+        assert info.algo == TCGEN05
+        c, dtc = dev.matmul(A, dt, B, dt, algo=TCGEN05)
+        exp, dte = R.oracle_matmul(A, dt, B, dt, "cuda")
+        assert_matches(c, dtc, exp, dte, what=f"dtype {dt} batch={batch} M={M} K={K} N={N}")
+    # aligned shape, but every buffer starts one element past a 16-byte boundary
+    es = R.NP[dt]().itemsize
+    M, K, N = 200, 64 * 3, 64 * 5
+    A = R.fill((M, K), dt, 901, F(dt)); B = R.fill((K, N), dt, 902, F(dt))
+    pa, pb, pc = dev.alloc(A.nbytes + 64), dev.alloc(B.nbytes + 64), dev.alloc(M * N * es + 64)
+    dev.check(dev.lib.tvb_memcpy_h2d(0, pa + es, A.ctypes.data, A.nbytes, None))
+    dev.check(dev.lib.tvb_memcpy_h2d(0, pb + es, B.ctypes.data, B.nbytes, None))
+    dev.sync()
+    dev.matmul_ptr(pa + es, dt, pb + es, dt, pc + es, 1, M, K, N, algo=TCGEN05)
+    dev.sync()
+    got = dev.download(pc, (M, N), dt, offset_bytes=es)
+    exp, dte = R.oracle_matmul(A, dt, B, dt, "cuda")
+    assert_matches(got, dt, exp, dte, what=f"dtype {dt} unaligned buffers")
+    for p in (pa, pb, pc):
+        dev.free(p)
+
+
+def test_kernel_choice(dev, tv):
+    # other dtype pairs run on the CUDA-core kernel; forcing the tensor-core path on them fails
+    info = tv.ops.plan(R.INT16, R.INT16, 1, 64, 64, 64)
     assert info.algo == SIMT
-    c, dtc = dev.matmul(A, R.BFLOAT16, B, R.BFLOAT16, algo=AUTO)
-    exp, dte = R.oracle_matmul(A, R.BFLOAT16, B, R.BFLOAT16, "cuda")
-    assert_matches(c, dtc, exp, dte)
+    A = R.fill((50, 32), R.INT16, 1, 1); B = R.fill((32, 48), R.INT16, 2, 1)
     with pytest.raises(tv._lib.TvbError) as e:
-        dev.matmul(A, R.BFLOAT16, B, R.BFLOAT16, algo=TCGEN05)
+        dev.matmul(A, R.INT16, B, R.INT16, algo=TCGEN05)
     assert e.value.code == 9
-    info = tv.ops.plan(R.BFLOAT16, R.BFLOAT16, 1, 4096, 4096, 4096)
     # large problems run on CTA pairs (256 x 256 tiles, 128 elements of K per stage) ...
+    info = tv.ops.plan(R.BFLOAT16, R.BFLOAT16, 1, 4096, 4096, 4096)
     assert (info.algo, info.tile_m, info.tile_n, info.tile_k, info.passes) == (TCGEN05, 256, 256, 128, 1)
     # ... small ones keep one CTA per 128-row tile so that more SMs have work
     info = tv.ops.plan(R.BFLOAT16, R.BFLOAT16, 1, 1024, 1024, 1024)
