@@ -4,6 +4,8 @@
 #include <cuda_fp16.h>
 #include <stdint.h>
 
+#include <type_traits>
+
 namespace tvb {
 
 // ---- fp32 -> (hi, lo) TF32 split ----------------------------------------------------
@@ -44,18 +46,28 @@ split_tf32_kernel(const float4* __restrict__ x, float4* __restrict__ hi, float4*
   }
 }
 
-// The split for operands whose rows do not start on 16-byte boundaries (K not a multiple of 4,
-// or an unaligned base): one element per thread, destination rows padded to `kp` floats so that
-// TMA can address them.  src is [rows][k] dense, hi/lo are [rows][kp].
+// Element of any dtype that promotes to a float accumulator -> float, exactly as
+// static_cast<float>(x) does in the reference kernel (mul.cu:41).
+template <typename T>
+__device__ __forceinline__ float elem_to_f32(T x) {
+  if constexpr (std::is_same_v<T, __half>) return __half2float(x);
+  else if constexpr (std::is_same_v<T, __nv_bfloat16>) return __bfloat162float(x);
+  else return static_cast<float>(x);
+}
+
+// The general split: source elements of type T (fp32, or a type that the product promotes to
+// float: int8/16/32, f16, bf16), one element per thread, destination rows padded to `kp` floats
+// so that TMA can address them.  src is [rows][k] dense, hi/lo are [rows][kp].
+template <typename T>
 static __global__ void __launch_bounds__(256)
-split_tf32_rows_kernel(const float* __restrict__ src, float* __restrict__ hi, float* __restrict__ lo,
+split_tf32_rows_kernel(const T* __restrict__ src, float* __restrict__ hi, float* __restrict__ lo,
                        size_t rows, int k, int kp) {
   const size_t total = rows * static_cast<size_t>(k);
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
   for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
     const size_t r = i / k;
     const int c = static_cast<int>(i - r * k);
-    const float v = src[i];
+    const float v = elem_to_f32(src[i]);
     const float h = round_tf32(v);
     hi[r * kp + c] = h;
     lo[r * kp + c] = round_tf32(v - h);
@@ -85,8 +97,9 @@ pad_rows_kernel(const unsigned char* __restrict__ src, unsigned char* __restrict
 // Same split for the B operand, written transposed: src is [batch][K][N], hi and lo are
 // [batch][N][kp] (kp >= K, rows padded to 16 bytes), so the tensor core can read B K-major.  32x32 tiles go through shared
 // memory: reads are coalesced along N, writes along K.  grid = (ceil(N/32), ceil(K/32), batch).
+template <typename T>
 static __global__ void __launch_bounds__(256)
-split_tf32_transpose_kernel(const float* __restrict__ src, float* __restrict__ hi,
+split_tf32_transpose_kernel(const T* __restrict__ src, float* __restrict__ hi,
                             float* __restrict__ lo, int K, int N, int kp) {
   __shared__ float th[32][33];
   __shared__ float tl[32][33];
@@ -99,7 +112,7 @@ split_tf32_transpose_kernel(const float* __restrict__ src, float* __restrict__ h
     const int k = k0 + ty + 8 * j, n = n0 + tx;
     float h = 0.f, l = 0.f;
     if (k < K && n < N) {
-      const float v = src[boff + static_cast<size_t>(k) * N + n];
+      const float v = elem_to_f32(src[boff + static_cast<size_t>(k) * N + n]);
       h = round_tf32(v);
       l = round_tf32(v - h);
     }

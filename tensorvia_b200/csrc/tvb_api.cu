@@ -189,6 +189,13 @@ const SimtLaunch g_simt[8][8] = {TVB_SIMT_ROW(0), TVB_SIMT_ROW(1), TVB_SIMT_ROW(
 constexpr int kPairStages = 3;   // stages of the CTA-pair kernel
 constexpr int kPairKAtoms = 2;   // 128-byte K atoms per stage of the CTA-pair kernel
 
+// dtypes whose products accumulate in float and give a FLOAT32 result: they can share the fp32
+// tensor-core path by being converted to float inside its split pass
+inline bool promotes_to_f32(int dt) {
+  return dt == TVB_INT8 || dt == TVB_INT16 || dt == TVB_INT32 || dt == TVB_BFLOAT16 || dt == TVB_FLOAT16 ||
+         dt == TVB_FLOAT32;
+}
+
 struct UmmaPlan {
   int op = -1;        // OP_*
   int block_n = 256;
@@ -203,8 +210,13 @@ struct UmmaPlan {
 // Problems the tensor-core kernels take: same-dtype f16 / bf16 / int8 / fp32 of any shape.
 bool umma_eligible(int dta, int dtb, int64_t batch, int64_t M, int64_t K, int64_t N, const void* A,
                    const void* B, const void* C, UmmaPlan* plan) {
-  if (dta != dtb) return false;
   UmmaPlan p;
+  if (dta != dtb) {
+    // mixed pairs whose result is FLOAT32 (int8 x f16, bf16 x f16, int32 x fp32, ...): both
+    // operands are converted to float by the split pass and multiplied as fp32
+    if (!(promotes_to_f32(dta) && promotes_to_f32(dtb) && compute_type_of(dta, dtb) == TVB_FLOAT32)) return false;
+    dta = TVB_FLOAT32;
+  }
   switch (dta) {
     case TVB_FLOAT16: p.op = OP_F16; p.es = 2; p.tm_type = CU_TENSOR_MAP_DATA_TYPE_FLOAT16; break;
     case TVB_BFLOAT16: p.op = OP_BF16; p.es = 2; p.tm_type = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16; break;
@@ -383,8 +395,58 @@ int ensure_workspace(Context* c, size_t bytes, cudaStream_t s) {
   return TVB_OK;
 }
 
-int run_umma(Context* c, const UmmaPlan& plan, const void* A, const void* B, void* C, int64_t batch,
-             int64_t M, int64_t K, int64_t N, cudaStream_t s) {
+template <typename T>
+cudaError_t launch_split_rows_t(Context* c, const void* src, float* hi, float* lo, size_t rows, int k, int kp,
+                                cudaStream_t s) {
+  size_t blocks = (rows * static_cast<size_t>(k) + 255) / 256;
+  const size_t cap = static_cast<size_t>(c->sm_count) * 16;
+  if (blocks > cap) blocks = cap;
+  if (blocks == 0) blocks = 1;
+  split_tf32_rows_kernel<T><<<static_cast<unsigned>(blocks), 256, 0, s>>>(static_cast<const T*>(src), hi, lo, rows, k, kp);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError();
+}
+cudaError_t launch_split_rows(Context* c, int dtype, const void* src, float* hi, float* lo, size_t rows, int k,
+                              int kp, cudaStream_t s) {
+  switch (dtype) {
+    case TVB_INT8: return launch_split_rows_t<int8_t>(c, src, hi, lo, rows, k, kp, s);
+    case TVB_INT16: return launch_split_rows_t<int16_t>(c, src, hi, lo, rows, k, kp, s);
+    case TVB_INT32: return launch_split_rows_t<int32_t>(c, src, hi, lo, rows, k, kp, s);
+    case TVB_BFLOAT16: return launch_split_rows_t<__nv_bfloat16>(c, src, hi, lo, rows, k, kp, s);
+    case TVB_FLOAT16: return launch_split_rows_t<__half>(c, src, hi, lo, rows, k, kp, s);
+    default: return launch_split_rows_t<float>(c, src, hi, lo, rows, k, kp, s);
+  }
+}
+template <typename T>
+cudaError_t launch_split_transpose_t(const void* src, float* hi, float* lo, int64_t batch, int K, int N, int kp,
+                                     cudaStream_t s) {
+  // B [batch][K][N] -> hi/lo [batch][N][kp]; gridDim.z carries at most 65535 batches per launch
+  for (int64_t b0 = 0; b0 < batch; b0 += 65535) {
+    const int nbz = static_cast<int>(batch - b0 < 65535 ? batch - b0 : 65535);
+    dim3 grid(static_cast<unsigned>((N + 31) / 32), static_cast<unsigned>((K + 31) / 32), nbz);
+    split_tf32_transpose_kernel<T><<<grid, 256, 0, s>>>(
+        static_cast<const T*>(src) + static_cast<size_t>(b0) * K * N, hi + static_cast<size_t>(b0) * N * kp,
+        lo + static_cast<size_t>(b0) * N * kp, K, N, kp);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+  }
+  return cudaSuccess;
+}
+cudaError_t launch_split_transpose(int dtype, const void* src, float* hi, float* lo, int64_t batch, int K, int N,
+                                   int kp, cudaStream_t s) {
+  switch (dtype) {
+    case TVB_INT8: return launch_split_transpose_t<int8_t>(src, hi, lo, batch, K, N, kp, s);
+    case TVB_INT16: return launch_split_transpose_t<int16_t>(src, hi, lo, batch, K, N, kp, s);
+    case TVB_INT32: return launch_split_transpose_t<int32_t>(src, hi, lo, batch, K, N, kp, s);
+    case TVB_BFLOAT16: return launch_split_transpose_t<__nv_bfloat16>(src, hi, lo, batch, K, N, kp, s);
+    case TVB_FLOAT16: return launch_split_transpose_t<__half>(src, hi, lo, batch, K, N, kp, s);
+    default: return launch_split_transpose_t<float>(src, hi, lo, batch, K, N, kp, s);
+  }
+}
+
+int run_umma(Context* c, const UmmaPlan& plan, int dta, int dtb, const void* A, const void* B, void* C,
+             int64_t batch, int64_t M, int64_t K, int64_t N, cudaStream_t s) {
   const size_t es = plan.es;
   const uint32_t atom_k = static_cast<uint32_t>(128 / es);  // K elements per 128-byte swizzle atom
   // K elements per pipeline stage, and the K rows of one MN-major B box
@@ -445,28 +507,15 @@ int run_umma(Context* c, const UmmaPlan& plan, const void* A, const void* B, voi
     float* alo = reinterpret_cast<float*>(w + na_b);
     float* bhi = reinterpret_cast<float*>(w + 2 * na_b);
     float* blo = reinterpret_cast<float*>(w + 2 * na_b + nb_b);
-    if (kp == static_cast<size_t>(K) && !misaligned(A)) {
-      TVB_CUDA(launch_split(c, A, ahi, alo, na, s));
+    if (dta == TVB_FLOAT32 && kp == static_cast<size_t>(K) && !misaligned(A)) {
+      TVB_CUDA(launch_split(c, A, ahi, alo, na, s));   // 16-byte vector loads
     } else {
-      const size_t rows = static_cast<size_t>(batch) * M;
-      size_t blocks = (rows * K + 255) / 256;
-      const size_t cap = static_cast<size_t>(c->sm_count) * 16;
-      if (blocks > cap) blocks = cap;
-      split_tf32_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(
-          static_cast<const float*>(A), ahi, alo, rows, static_cast<int>(K), static_cast<int>(kp));
-      g_launches.fetch_add(1, std::memory_order_relaxed);
-      TVB_CUDA(cudaGetLastError());
+      TVB_CUDA(launch_split_rows(c, dta, A, ahi, alo, static_cast<size_t>(batch) * M, static_cast<int>(K),
+                                 static_cast<int>(kp), s));
     }
     // B is split and transposed to [batch][N][kp] in the same pass
-    for (int64_t b0 = 0; b0 < batch; b0 += 65535) {
-      const int nbz = static_cast<int>(batch - b0 < 65535 ? batch - b0 : 65535);
-      dim3 grid(static_cast<unsigned>((N + 31) / 32), static_cast<unsigned>((K + 31) / 32), nbz);
-      split_tf32_transpose_kernel<<<grid, 256, 0, s>>>(
-          static_cast<const float*>(B) + static_cast<size_t>(b0) * K * N, bhi + static_cast<size_t>(b0) * N * kp,
-          blo + static_cast<size_t>(b0) * N * kp, static_cast<int>(K), static_cast<int>(N), static_cast<int>(kp));
-      g_launches.fetch_add(1, std::memory_order_relaxed);
-      TVB_CUDA(cudaGetLastError());
-    }
+    TVB_CUDA(launch_split_transpose(dtb, B, bhi, blo, batch, static_cast<int>(K), static_cast<int>(N),
+                                    static_cast<int>(kp), s));
     a_hi = ahi; a_lo = alo; b_hi = bhi; b_lo = blo;
     pitch_a = kp;
     pitch_b = kp;
@@ -619,9 +668,10 @@ int matmul_impl(int device, const void* A, const void* B, void* C, int dta, int 
   const bool can_umma = umma_eligible(dta, dtb, batch, M, K, N, A, B, C, &plan);
   if (algo == TVB_ALGO_TCGEN05 && !can_umma)
     return fail(TVB_ERR_UNSUPPORTED,
-                "the tcgen05 path takes f16 x f16, bf16 x bf16, int8 x int8 and fp32 x fp32 only");
+                "the tcgen05 path takes f16 x f16, bf16 x bf16, int8 x int8, fp32 x fp32 and the mixed pairs "
+                "whose result is FLOAT32");
   if (can_umma && algo != TVB_ALGO_SIMT) {
-    rc = run_umma(c, plan, A, B, C, batch, M, K, N, s);
+    rc = run_umma(c, plan, dta, dtb, A, B, C, batch, M, K, N, s);
     if (rc == TVB_OK || algo == TVB_ALGO_TCGEN05 || rc != TVB_ERR_UNSUPPORTED) return rc;
     // a tensor map the driver would not encode: fall through to the SIMT kernel
   }

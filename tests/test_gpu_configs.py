@@ -256,7 +256,8 @@ def test_torch_facing_operator(tv):
     ch = tv.matmul(ai, bh)
     torch.cuda.synchronize()
     assert ch.dtype == torch.float32
-    assert torch.allclose(ch, ai.float() @ bh.float(), rtol=1e-4, atol=1e-4)
+    want = ai.double() @ bh.double()
+    assert (torch.linalg.norm(ch.double() - want) / torch.linalg.norm(want)).item() <= 1e-5
 
 
 def test_cpp_host_layer_on_gpu(tv):

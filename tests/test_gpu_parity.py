@@ -228,3 +228,25 @@ def test_shared_tiles_of_an_incomplete_wave(dev, tv, monkeypatch):
     assert_matches(c3, dtc, exp, dte, what="bf16 whole tiles")
     # the two schedules add the same products in a different order: equal to fp32 rounding
     assert R.rel_frobenius(c1, c3, R.BFLOAT16) < 1e-3
+
+
+MIXED_F32 = [(a, b) for a in (R.INT8, R.INT16, R.INT32, R.BFLOAT16, R.FLOAT16, R.FLOAT32)
+             for b in (R.INT8, R.INT16, R.INT32, R.BFLOAT16, R.FLOAT16, R.FLOAT32)
+             if a != b and R.oracle().tvo_compute_type(a, b) == R.FLOAT32]
+
+
+@pytest.mark.parametrize("a,b", MIXED_F32)
+def test_mixed_pairs_with_float32_result_on_tensor_cores(dev, tv, a, b):
+    """int8 x f16, bf16 x f16, int32 x fp32, ...: the reference multiplies them in a float
+    accumulator (mul.cu:19) and returns FLOAT32; here both operands are converted to float inside
+    the fp32 path's split pass and run as 3xTF32."""
+    assert len(MIXED_F32) == 24
+    info = tv.ops.plan(a, b, 1, 300, 520, 264)
+    assert info.algo == TCGEN05 and info.passes == 3
+    A = R.fill((2, 300, 520), a, 40 + a, F(a)); B = R.fill((2, 520, 264), b, 50 + b, F(b))
+    c, dtc = dev.matmul(A, a, B, b)
+    exp, dte = R.oracle_matmul(A, a, B, b, "cuda")
+    assert dtc == R.FLOAT32
+    assert_matches(c, dtc, exp, dte, what=f"{R.DTYPE_NAMES[a]} x {R.DTYPE_NAMES[b]}")
+    c2, _ = dev.matmul(A, a, B, b, algo=SIMT)
+    assert_matches(c, dtc, c2, dtc, what="tensor-core vs CUDA-core kernel")
