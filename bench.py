@@ -241,6 +241,17 @@ def gpu_arm(args):
     cfg_name = args.config
     cfg, dt, batch, M, K, N, dist_kind, es = CONFIGS[cfg_name]
     nb = batch or 1
+    strong = args.scaling == "strong" and world > 1
+    if strong:
+        # total work fixed: this rank's rows of A (2-D) or run of batches (3-D) of the ONE problem
+        if batch is None:
+            begin, count = ops.shard_range(M, 128, world, rank)
+            M = count
+        else:
+            begin, count = ops.shard_range(batch, 1, world, rank)
+            nb = count
+        if count == 0:
+            raise SystemExit("more ranks than shards")
     seed_a, seed_b = SEED_BASE + 2 * cfg, SEED_BASE + 2 * cfg + 1
     bytes_a, bytes_b, bytes_c = nb * M * K * es, nb * K * N * es, nb * M * N * es
     flops_rank = 2.0 * nb * M * K * N
@@ -261,9 +272,9 @@ def gpu_arm(args):
     for s in range(nsets):
         pa, pb, pc = dalloc(bytes_a), dalloc(bytes_b), dalloc(bytes_c)
         # rank r owns rows [r*M, (r+1)*M) of the global A (2-D) or its own run of batches (3-D)
-        first_a = rank * nb * M * K
+        first_a = (begin * (K if batch is None else M * K)) if strong else rank * nb * M * K
         check(lib.tvb_fill_splitmix(local, pa, dt, nb * M * K, seed_a + 16 * s, first_a, dist_kind, sp))
-        first_b = rank * nb * K * N if batch else 0
+        first_b = ((begin * K * N) if strong else rank * nb * K * N) if batch else 0
         check(lib.tvb_fill_splitmix(local, pb, dt, nb * K * N, seed_b + 16 * s, first_b, dist_kind, sp))
         sets.append((pa, pb, pc))
     torch.cuda.synchronize()
@@ -345,8 +356,13 @@ def gpu_arm(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_total, e2e_ms = float(t[0]), float(t[1])
     ms_step = ms_total / args.steps
-    value = world * flops_rank / (ms_step * 1e-3) / 1e12
-    e2e_value = world * flops_rank / (e2e_ms * 1e-3) / 1e12
+    flops_job = flops_rank * world
+    if strong:
+        t = torch.tensor([flops_rank], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t)          # shards may differ by a tile row
+        flops_job = float(t[0])
+    value = flops_job / (ms_step * 1e-3) / 1e12
+    e2e_value = flops_job / (e2e_ms * 1e-3) / 1e12
 
     if rank == 0:
         peaks = measured_peaks()
@@ -362,10 +378,10 @@ def gpu_arm(args):
         unit = "TOP/s" if dt == INT8 else "TFLOP/s"
         line = {
             "metric": "ops::matmul TFLOP/s", "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
-            "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if strong else "weak",
             "vs_baseline": None, "dtype": DTYPE_NAME[dt], "data": "synthetic",
             "config": {
-                "workload": WORKLOAD_TEXT[cfg_name], "config": cfg_name, "per_gpu": "one full problem per GPU" if world > 1 else "single GPU",
+                "workload": WORKLOAD_TEXT[cfg_name], "config": cfg_name, "per_gpu": ("1/%d of the problem per GPU" % world if strong else "one full problem per GPU") if world > 1 else "single GPU",
                 "parallelism": ("rows of A sharded, B replicated" if batch is None else "batches sharded") if world > 1 else "none",
                 "kernel": f"tcgen05 {info.tile_m}x{info.tile_n}x{info.tile_k}, {info.stages} stages, {info.ctas} CTAs, {info.passes} pass(es)" if info.algo == 1 else "simt",
                 "l2": f"{nsets} rotating operand sets ({nsets * per_set >> 20} MiB) exceed the {L2_BYTES >> 20} MiB L2",
@@ -439,6 +455,8 @@ def main():
     ap.add_argument("--config", default="c2", choices=sorted(CONFIGS))
     ap.add_argument("--impl", default="tensorvia_b200", choices=["tensorvia_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="weak (default): one full problem per GPU; strong: one problem, rows or batches split over the GPUs")
     args = ap.parse_args()
     if args.gpus > 1 and "WORLD_SIZE" not in os.environ and args.impl != "reference":
         # convenience: relaunch under torch.distributed.run, one rank per GPU
