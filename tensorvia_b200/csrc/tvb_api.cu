@@ -477,14 +477,15 @@ int run_umma(Context* c, const UmmaPlan& plan, int dta, int dtb, const void* A, 
     // memory to the tile's owner.  Handing a sum over costs about 4 us (measured: raw sums out
     // through L2, fence, flag, sums in), part of which the non-owning share hides by taking
     // fewer stages.  Against a tile time of 21 us at 32 stages the split gains 1.5 %, at 64
-    // stages 3.7 %, at 128 stages 5 %; it is used from 64 stages on.  (Not for fp32: its
-    // epilogue already sums K chunks in registers.)
+    // stages 3.7 %, at 128 stages 5 %; it is used from 64 stages on (fp32: 64 stage-passes).
     const uint32_t rest = total_tiles % pairs;
     const uint32_t kb = static_cast<uint32_t>(k_blocks);
     const uint32_t shift = kb / 16;
     const uint32_t kw = kb / 2 > shift ? kb / 2 - shift : 0;
-    if (plan.op != OP_TF32 && rest > 0 && 2 * rest <= pairs && kb >= 64 && kw >= 1 &&
-        static_cast<size_t>(rest) * 8 <= static_cast<size_t>(Context::kMaxFlags) &&
+    // stages x passes = MMA batches per tile: fp32 runs three per stage
+    const uint32_t work = kb * static_cast<uint32_t>(plan.passes);
+    if (rest > 0 && 2 * rest <= pairs && work >= 64 && kw >= 1 &&
+        static_cast<size_t>(rest) * 16 <= static_cast<size_t>(Context::kMaxFlags) &&
         getenv("TVB_NO_SPLIT_K") == nullptr) {
       sk_rest = rest;
       sk_kw = kw;
@@ -500,9 +501,9 @@ int run_umma(Context* c, const UmmaPlan& plan, int dta, int dtb, const void* A, 
     const size_t kp = round_up(static_cast<size_t>(K), 4);
     const size_t na = static_cast<size_t>(batch) * M * kp, nb = static_cast<size_t>(batch) * N * kp;
     const size_t na_b = round_up(na * 4, 256), nb_b = round_up(nb * 4, 256);
-    int rc = ensure_workspace(c, 2 * na_b + 2 * nb_b, s);
+    int rc = ensure_workspace(c, partial_bytes + 2 * na_b + 2 * nb_b, s);
     if (rc != TVB_OK) return rc;
-    char* w = static_cast<char*>(c->ws);
+    char* w = static_cast<char*>(c->ws) + partial_bytes;   // shared-tile sums sit at the front
     float* ahi = reinterpret_cast<float*>(w);
     float* alo = reinterpret_cast<float*>(w + na_b);
     float* bhi = reinterpret_cast<float*>(w + 2 * na_b);

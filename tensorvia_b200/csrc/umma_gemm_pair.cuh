@@ -217,9 +217,9 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_con
       bool ok = true;
       for (uint32_t item = pair; ok && item < p.total_items; item += num_pairs) {
         const PairItem w = decode_item(item, p);
-        // (the chunked fp32 path never shares a tile: its items always cover all of K)
+        // fp32 sums its item's stages in chunks of kc; the others in one go
         const int kc_item = CHUNKED ? kc : (w.kb_end - w.kb_begin);
-        const int chunks_item = CHUNKED ? chunks : 1;
+        const int chunks_item = (w.kb_end - w.kb_begin + kc_item - 1) / kc_item;
         for (int ch = 0; ok && ch < chunks_item; ++ch, ++local) {
           const uint32_t buf = local & 1u;
           const uint32_t acc_phase = (local >> 1) & 1u;
@@ -367,11 +367,20 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_con
       const int half = (warp - 2) >> 2;
       float acc[HALF_N];
       for (uint32_t item = pair; ok && item < p.total_items; item += num_pairs) {
-        const PairItem w = decode_item(item, p);   // never a shared tile on this path
+        const PairItem w = decode_item(item, p);
         const int b = w.b, mt = w.mt, nt = w.nt;
+        const int chunks_item = (w.kb_end - w.kb_begin + kc - 1) / kc;
+        // a shared partial result: [slot][cta rank][16-byte group of columns][row], see above
+        auto partial_vec = [&](uint32_t slot, int group) {
+          return reinterpret_cast<float4*>(p.partial) +
+                 ((static_cast<size_t>(slot) * 2 + rank) * (BLOCK_N / 4) + half * (HALF_N / 4) + group) * 128 +
+                 quad * 32 + lane;
+        };
+        // one flag per (slot, CTA, warp): eight epilogue warps here
+        auto flag_of = [&](uint32_t slot) { return p.flags + (static_cast<size_t>(slot) * 2 + rank) * 8 + (warp - 2); };
 #pragma unroll
         for (int j = 0; j < HALF_N; ++j) acc[j] = 0.f;
-        for (int ch = 0; ch < chunks; ++ch, ++local) {
+        for (int ch = 0; ch < chunks_item; ++ch, ++local) {
           const uint32_t buf = local & 1u;
           const uint32_t acc_phase = (local >> 1) & 1u;
           const bool landed = ptx::mbar_wait(tfull_bar(buf), acc_phase, p.wait_limit_ns);
@@ -396,6 +405,39 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_con
           if (lane == 0) ptx::mbar_arrive_cluster(tempty_bar_leader(buf));
         }
         if (!ok) break;
+        if (w.part >= 1) {
+          // not the tile's owner: hand this warp's sums over and go on
+#pragma unroll
+          for (int g = 0; g < HALF_N / 4; ++g)
+            *partial_vec(w.slot, g) = make_float4(acc[4 * g], acc[4 * g + 1], acc[4 * g + 2], acc[4 * g + 3]);
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) *reinterpret_cast<volatile uint32_t*>(flag_of(w.slot)) = p.epoch;
+          continue;
+        }
+        if (w.parts > 1) {
+          bool there = true;
+          if (lane == 0) {
+            const volatile uint32_t* f = reinterpret_cast<const volatile uint32_t*>(flag_of(w.slot));
+            const uint64_t t0 = ptx::globaltimer_ns();
+            while (*f != p.epoch) {
+              if (ptx::globaltimer_ns() - t0 > p.wait_limit_ns) { there = false; break; }
+              __nanosleep(200);
+            }
+            __threadfence();
+          }
+          there = __shfl_sync(0xffffffffu, there ? 1 : 0, 0) != 0;
+          if (!there) {
+            if (lane == 0) atomicOr(p.status, ST_EPILOGUE_TIMEOUT);
+            ok = false;
+            break;
+          }
+#pragma unroll
+          for (int g = 0; g < HALF_N / 4; ++g) {
+            const float4 u = __ldcg(partial_vec(w.slot, g));
+            acc[4 * g] += u.x; acc[4 * g + 1] += u.y; acc[4 * g + 2] += u.z; acc[4 * g + 3] += u.w;
+          }
+        }
         const int row = mt * Cfg::BLOCK_M + static_cast<int>(rank) * 128 + quad * 32 + lane;
         const int col0 = nt * BLOCK_N + half * HALF_N;
         if (row < p.M) {

@@ -250,3 +250,20 @@ def test_mixed_pairs_with_float32_result_on_tensor_cores(dev, tv, a, b):
     assert_matches(c, dtc, exp, dte, what=f"{R.DTYPE_NAMES[a]} x {R.DTYPE_NAMES[b]}")
     c2, _ = dev.matmul(A, a, B, b, algo=SIMT)
     assert_matches(c, dtc, c2, dtc, what="tensor-core vs CUDA-core kernel")
+
+
+def test_shared_tiles_fp32(dev, tv, monkeypatch):
+    """The same K-sharing for fp32 (its epilogue keeps the sums in registers across K chunks and
+    hands those over), on a shape that needs it and on configuration 1's shape, where it is
+    chosen by itself (176 tiles on 74 pairs leave a last wave of 28)."""
+    monkeypatch.setenv("TVB_CTA_PAIR", "1")
+    A = R.fill((300, 2200), R.FLOAT32, 61); B = R.fill((2200, 520), R.FLOAT32, 62)
+    exp, dte = R.oracle_matmul(A, R.FLOAT32, B, R.FLOAT32, "cuda")
+    c1, dtc = dev.matmul(A, R.FLOAT32, B, R.FLOAT32, algo=TCGEN05)
+    assert_matches(c1, dtc, exp, dte, what="fp32 shared tiles")
+    c2, _ = dev.matmul(A, R.FLOAT32, B, R.FLOAT32, algo=TCGEN05)
+    assert c1.tobytes() == c2.tobytes()
+    monkeypatch.setenv("TVB_NO_SPLIT_K", "1")
+    c3, _ = dev.matmul(A, R.FLOAT32, B, R.FLOAT32, algo=TCGEN05)
+    assert_matches(c3, dtc, exp, dte, what="fp32 whole tiles")
+    assert R.rel_frobenius(c1, c3, R.FLOAT32) < 1e-5
