@@ -477,14 +477,15 @@ int run_umma(Context* c, const UmmaPlan& plan, int dta, int dtb, const void* A, 
     // memory to the tile's owner.  Handing a sum over costs about 4 us (measured: raw sums out
     // through L2, fence, flag, sums in), part of which the non-owning share hides by taking
     // fewer stages.  Against a tile time of 21 us at 32 stages the split gains 1.5 %, at 64
-    // stages 3.7 %, at 128 stages 5 %; it is used from 64 stages on (fp32: 64 stage-passes).
+    // stages 3.7 %, at 128 stages 5 %, and at 16 stages it loses 2 %; it is used from 32 stages
+    // on (fp32: 32 stage-passes).
     const uint32_t rest = total_tiles % pairs;
     const uint32_t kb = static_cast<uint32_t>(k_blocks);
     const uint32_t shift = kb / 16;
     const uint32_t kw = kb / 2 > shift ? kb / 2 - shift : 0;
     // stages x passes = MMA batches per tile: fp32 runs three per stage
     const uint32_t work = kb * static_cast<uint32_t>(plan.passes);
-    if (rest > 0 && 2 * rest <= pairs && work >= 64 && kw >= 1 &&
+    if (rest > 0 && 2 * rest <= pairs && work >= 32 && kw >= 1 &&
         static_cast<size_t>(rest) * 16 <= static_cast<size_t>(Context::kMaxFlags) &&
         getenv("TVB_NO_SPLIT_K") == nullptr) {
       sk_rest = rest;
