@@ -239,11 +239,12 @@ bool umma_eligible(int dta, int dtb, int64_t batch, int64_t M, int64_t K, int64_
     if (v == 128 || v == 256) p.block_n = v;
   }
   p.stages = (p.block_n == 256) ? 4 : 6;
-  // CTA pairs once there are enough 256x256 tiles to occupy every pair of SMs; smaller
-  // problems keep one CTA per 128-row tile so that more SMs have work (TVB_CTA_PAIR overrides)
+  // CTA pairs whenever the problem has more than one 128-row tile and wide tiles: a pair runs
+  // its MMAs at 128 cycles against ~185 for one CTA per tile (shared-memory bound), which
+  // outweighs leaving some pairs idle on small problems (measured from 256x256 outputs up:
+  // 2048^3 19.6 vs 20.6 us, 1024x4096x1024 23.0 vs 29.4 us).  TVB_CTA_PAIR overrides.
   {
-    const int64_t pair_tiles = batch * ((M + 255) / 256) * ((N + 255) / 256);
-    p.pair = p.block_n == 256 && M > 128 && pair_tiles >= 74;
+    p.pair = p.block_n == 256 && M > 128;
     if (const char* e = getenv("TVB_CTA_PAIR")) p.pair = p.block_n == 256 && atoi(e) != 0;
     if (p.pair) {
       p.tile_m = 256;

@@ -113,6 +113,9 @@ struct UmmaEpilogue {
   static constexpr int WARPS = CHUNKED ? 8 : 4;
 };
 
+// words of the per-warp staging area of store_block_staged (32 rows x 33: conflict-free both ways)
+constexpr int kStageWords = 32 * 33;
+
 template <int OP, int BLOCK_N, int STAGES>
 struct UmmaGemmConfig {
   static constexpr int BLOCK_M = 128;
@@ -120,9 +123,10 @@ struct UmmaGemmConfig {
   static constexpr int B_BYTES = BLOCK_N * 128;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int NUM_BARRIERS = 2 * STAGES + 4;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + NUM_BARRIERS * 8 + 16 + 1024;
-  static constexpr int TMEM_COLS = 2 * BLOCK_N;
   static constexpr int EPI_WARPS = UmmaEpilogue<OP>::WARPS;
+  static constexpr int STAGING_BYTES = EPI_WARPS * kStageWords * 4;   // for unaligned C, see store_block_staged
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + NUM_BARRIERS * 8 + 16 + STAGING_BYTES + 1024;
+  static constexpr int TMEM_COLS = 2 * BLOCK_N;
   static constexpr int THREADS = 64 + 32 * EPI_WARPS;
 };
 
@@ -197,26 +201,31 @@ __device__ __forceinline__ void store_row_chunk(typename OpTraits<OP>::Out* dst,
   }
 }
 
-// The same for a C whose rows are not 16-byte aligned (N odd, or an unaligned base): one
-// element per store.
+// The same for a C whose rows are not 16-byte aligned (N odd, or an unaligned base), where
+// 16-byte stores are impossible.  Each lane holds 32 columns of ITS row; storing them directly
+// would put the 32 lanes of every store on 32 different rows.  The 32x32 block therefore goes
+// through a 32x33-word staging area of the warp in shared memory and comes back transposed:
+// every store then writes 32 consecutive elements of one row.
 template <int OP>
-__device__ __forceinline__ void store_row_chunk_any(typename OpTraits<OP>::Out* dst, const uint32_t (&v)[32],
-                                                    int cols_left) {
+__device__ __forceinline__ void store_block_staged(uint32_t* stage, const uint32_t (&v)[32],
+                                                   typename OpTraits<OP>::Out* c_batch, int ldc, int row0,
+                                                   int col, int M, int N, int lane) {
 #pragma unroll
-  for (int j = 0; j < 32; ++j) {
-    if (j < cols_left) {
-      if constexpr (OP == OP_TF32) dst[j] = __uint_as_float(v[j]);
-      else if constexpr (OP == OP_F16) dst[j] = __float2half_rn(__uint_as_float(v[j]));
-      else if constexpr (OP == OP_BF16) dst[j] = __float2bfloat16_rn(__uint_as_float(v[j]));
-      else dst[j] = static_cast<int8_t>(v[j] & 0xFFu);
+  for (int j = 0; j < 32; ++j) stage[lane * 33 + j] = v[j];
+  __syncwarp();
+  const bool col_ok = col + lane < N;
+#pragma unroll 4
+  for (int r = 0; r < 32; ++r) {
+    const uint32_t x = stage[r * 33 + lane];
+    if (col_ok && row0 + r < M) {
+      typename OpTraits<OP>::Out* d = c_batch + static_cast<size_t>(row0 + r) * ldc + col + lane;
+      if constexpr (OP == OP_TF32) *d = __uint_as_float(x);
+      else if constexpr (OP == OP_F16) *d = __float2half_rn(__uint_as_float(x));
+      else if constexpr (OP == OP_BF16) *d = __float2bfloat16_rn(__uint_as_float(x));
+      else *d = static_cast<int8_t>(x & 0xFFu);
     }
   }
-}
-template <int OP>
-__device__ __forceinline__ void store_row_chunk_sel(typename OpTraits<OP>::Out* dst, const uint32_t (&v)[32],
-                                                    int cols_left, bool vec) {
-  if (vec) store_row_chunk<OP>(dst, v, cols_left);
-  else store_row_chunk_any<OP>(dst, v, cols_left);
+  __syncwarp();
 }
 
 template <int OP, int BLOCK_N, int STAGES>
@@ -256,6 +265,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
   const uint32_t slot_addr = bar_base + 8u * Cfg::NUM_BARRIERS;
   volatile uint32_t* slot_ptr =
       reinterpret_cast<volatile uint32_t*>(smem_raw + (slot_addr - raw_addr));
+  uint32_t* const staging = reinterpret_cast<uint32_t*>(smem_raw + (slot_addr + 16 - raw_addr));
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -408,8 +418,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
           ptx::tmem_ld_32x32(taddr + c * 64 + 32, v1);
           ptx::tmem_ld_wait();
           const int cols_left = p.N - (col0 + c * 64);
-          if (row < p.M && cols_left > 0) store_row_chunk_sel<OP>(crow + c * 64, v0, cols_left, p.c_vec != 0);
-          if (row < p.M && cols_left > 32) store_row_chunk_sel<OP>(crow + c * 64 + 32, v1, cols_left - 32, p.c_vec != 0);
+          if (p.c_vec != 0) {
+            if (row < p.M && cols_left > 0) store_row_chunk<OP>(crow + c * 64, v0, cols_left);
+            if (row < p.M && cols_left > 32) store_row_chunk<OP>(crow + c * 64 + 32, v1, cols_left - 32);
+          } else {
+            uint32_t* st = staging + (warp - 2) * kStageWords;
+            Out* cb = Cbase + static_cast<size_t>(b) * p.M * p.N;
+            const int row0 = mt * BLOCK_M + quad * 32;
+            store_block_staged<OP>(st, v0, cb, p.N, row0, col0 + c * 64, p.M, p.N, lane);
+            store_block_staged<OP>(st, v1, cb, p.N, row0, col0 + c * 64 + 32, p.M, p.N, lane);
+          }
         }
         ptx::tc_fence_before();
         ptx::mbar_arrive(tempty_bar(buf));
@@ -460,10 +478,18 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
             for (int g = 0; g < HALF_N / 4; ++g)
               if (col0 + g * 4 < p.N)
                 crow[g] = make_float4(acc[4 * g], acc[4 * g + 1], acc[4 * g + 2], acc[4 * g + 3]);
-          } else {
+          }
+        }
+        if (p.c_vec == 0) {
+          uint32_t* st = staging + (warp - 2) * kStageWords;
+          float* cb = reinterpret_cast<float*>(Cbase) + static_cast<size_t>(b) * p.M * p.N;
+          const int row0 = mt * BLOCK_M + quad * 32;
 #pragma unroll
-            for (int j = 0; j < HALF_N; ++j)
-              if (col0 + j < p.N) cf[j] = acc[j];
+          for (int c = 0; c < HALF_N / 32; ++c) {
+            uint32_t v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(acc[c * 32 + j]);
+            store_block_staged<OP>(st, v, cb, p.N, row0, col0 + c * 32, p.M, p.N, lane);
           }
         }
       }

@@ -38,9 +38,10 @@ struct UmmaPairConfig {
   static constexpr int B_BYTES = 128 * 128 * KATOMS;   // per CTA and stage (half of the B tile)
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int NUM_BARRIERS = 2 * STAGES + 4;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + NUM_BARRIERS * 8 + 16 + 1024;
-  static constexpr int TMEM_COLS = 2 * BLOCK_N;
   static constexpr int EPI_WARPS = UmmaEpilogue<OP>::WARPS;
+  static constexpr int STAGING_BYTES = EPI_WARPS * kStageWords * 4;   // for unaligned C, see store_block_staged
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + NUM_BARRIERS * 8 + 16 + STAGING_BYTES + 1024;
+  static constexpr int TMEM_COLS = 2 * BLOCK_N;
   static constexpr int THREADS = 64 + 32 * EPI_WARPS;
 };
 
@@ -120,6 +121,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_con
   auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
   const uint32_t slot_addr = bar_base + 8u * Cfg::NUM_BARRIERS;
   volatile uint32_t* slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (slot_addr - raw_addr));
+  uint32_t* const staging = reinterpret_cast<uint32_t*>(smem_raw + (slot_addr + 16 - raw_addr));
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -354,8 +356,16 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_con
               }
             }
             const int cols_left = p.N - (col0 + c * 64);
-            if (row < p.M && cols_left > 0) store_row_chunk_sel<OP>(crow + c * 64, v0, cols_left, p.c_vec != 0);
-            if (row < p.M && cols_left > 32) store_row_chunk_sel<OP>(crow + c * 64 + 32, v1, cols_left - 32, p.c_vec != 0);
+            if (p.c_vec != 0) {
+              if (row < p.M && cols_left > 0) store_row_chunk<OP>(crow + c * 64, v0, cols_left);
+              if (row < p.M && cols_left > 32) store_row_chunk<OP>(crow + c * 64 + 32, v1, cols_left - 32);
+            } else {
+              uint32_t* st = staging + (warp - 2) * kStageWords;
+              Out* cb = Cbase + static_cast<size_t>(b) * p.M * p.N;
+              const int row0 = row - lane;
+              store_block_staged<OP>(st, v0, cb, p.N, row0, col0 + c * 64, p.M, p.N, lane);
+              store_block_staged<OP>(st, v1, cb, p.N, row0, col0 + c * 64 + 32, p.M, p.N, lane);
+            }
           }
         }
         ptx::tc_fence_before();
@@ -449,10 +459,17 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_con
             for (int g = 0; g < HALF_N / 4; ++g)
               if (col0 + g * 4 < p.N)
                 crow[g] = make_float4(acc[4 * g], acc[4 * g + 1], acc[4 * g + 2], acc[4 * g + 3]);
-          } else {
+          }
+        }
+        if (p.c_vec == 0) {
+          uint32_t* st = staging + (warp - 2) * kStageWords;
+          float* cb = reinterpret_cast<float*>(Cbase) + static_cast<size_t>(b) * p.M * p.N;
 #pragma unroll
-            for (int j = 0; j < HALF_N; ++j)
-              if (col0 + j < p.N) cf[j] = acc[j];
+          for (int c = 0; c < HALF_N / 32; ++c) {
+            uint32_t v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(acc[c * 32 + j]);
+            store_block_staged<OP>(st, v, cb, p.N, row - lane, col0 + c * 32, p.M, p.N, lane);
           }
         }
       }

@@ -150,9 +150,11 @@ def test_kernel_choice(dev, tv):
     # large problems run on CTA pairs (256 x 256 tiles, 128 elements of K per stage) ...
     info = tv.ops.plan(R.BFLOAT16, R.BFLOAT16, 1, 4096, 4096, 4096)
     assert (info.algo, info.tile_m, info.tile_n, info.tile_k, info.passes) == (TCGEN05, 256, 256, 128, 1)
-    # ... small ones keep one CTA per 128-row tile so that more SMs have work
-    info = tv.ops.plan(R.BFLOAT16, R.BFLOAT16, 1, 1024, 1024, 1024)
+    # ... problems of at most 128 rows or 128 columns keep one CTA per tile
+    info = tv.ops.plan(R.BFLOAT16, R.BFLOAT16, 1, 128, 1024, 1024)
     assert (info.algo, info.tile_m, info.tile_n, info.tile_k) == (TCGEN05, 128, 256, 64)
+    info = tv.ops.plan(R.BFLOAT16, R.BFLOAT16, 1, 1024, 1024, 128)
+    assert (info.algo, info.tile_m, info.tile_n, info.tile_k) == (TCGEN05, 128, 128, 64)
     info = tv.ops.plan(R.FLOAT32, R.FLOAT32, 1, 2592, 2048, 4096)
     assert info.algo == TCGEN05 and info.passes == 3 and info.workspace_bytes > 0
 
@@ -211,7 +213,6 @@ def test_shared_tiles_of_an_incomplete_wave(dev, tv, monkeypatch):
     tiles is computed by two SM pairs over two ranges of K, one handing its raw sums to the
     other through scratch memory.  int8 must stay bit-exact, bf16 within tolerance; a second
     run must reproduce the first (the hand-over flags carry a per-launch epoch)."""
-    monkeypatch.setenv("TVB_CTA_PAIR", "1")   # these shapes are below the size that picks pairs by itself
     A = R.fill((512, 16384), R.INT8, 31, 1); B = R.fill((16384, 512), R.INT8, 32, 1)
     want = (A.astype(np.int32) @ B.astype(np.int32)).astype(np.int8)
     for _ in range(2):
@@ -256,7 +257,6 @@ def test_shared_tiles_fp32(dev, tv, monkeypatch):
     """The same K-sharing for fp32 (its epilogue keeps the sums in registers across K chunks and
     hands those over), on a shape that needs it and on configuration 1's shape, where it is
     chosen by itself (176 tiles on 74 pairs leave a last wave of 28)."""
-    monkeypatch.setenv("TVB_CTA_PAIR", "1")
     A = R.fill((300, 2200), R.FLOAT32, 61); B = R.fill((2200, 520), R.FLOAT32, 62)
     exp, dte = R.oracle_matmul(A, R.FLOAT32, B, R.FLOAT32, "cuda")
     c1, dtc = dev.matmul(A, R.FLOAT32, B, R.FLOAT32, algo=TCGEN05)
