@@ -135,6 +135,25 @@ int tvb_matmul(int device, const void* A, const void* B, void* C,
 int tvb_matmul_algo(int device, const void* A, const void* B, void* C,
                     int dtype_a, int dtype_b, int dtype_c,
                     int64_t batch, int64_t M, int64_t K, int64_t N, void* stream, int algo);
+/* The same product for operands that are VIEWS: element (b, m, k) of A is
+ * A[b*a_strides[0] + m*a_strides[1] + k*a_strides[2]] and element (b, k, n) of B is
+ * B[b*b_strides[0] + k*b_strides[1] + n*b_strides[2]] (strides in elements, none negative;
+ * A and B point at the view's first element, i.e. storage base + Metadata::offset).  This is
+ * what Tensor::t(), Tensor::permute() and Tensor::slice() produce (src/tensor.cpp:217-283):
+ * the reference's operator ignores Metadata::strides and multiplies the underlying buffer as
+ * if it were dense (src/backend/cuda/mul.cu:53-56), so a caller there has to materialise the
+ * view with contiguous() (src/tensor.cpp:303-310, repack.cu:5-54) first; here the view is
+ * consumed as it lies.  The result equals tvb_matmul on contiguous copies of the views.
+ * C is dense [batch, M, N].  On the tensor-core path an operand with unit stride along one of
+ * its two matrix indices is read in place (a transposed view only flips the operand's
+ * major-ness bit in the MMA instruction descriptor) provided its other stride, its batch
+ * stride and its base are multiples of 16 bytes; any other view costs one gathering copy
+ * into scratch memory.  `algo` as in tvb_matmul_algo. */
+int tvb_matmul_strided(int device, const void* A, const void* B, void* C,
+                       int dtype_a, int dtype_b, int dtype_c,
+                       int64_t batch, int64_t M, int64_t K, int64_t N,
+                       const int64_t a_strides[3], const int64_t b_strides[3],
+                       void* stream, int algo);
 /* What tvb_matmul would run for this problem. */
 int tvb_matmul_plan(int device, int dtype_a, int dtype_b,
                     int64_t batch, int64_t M, int64_t K, int64_t N, int algo,

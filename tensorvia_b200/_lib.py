@@ -67,6 +67,8 @@ SIGNATURES = {
     "tvb_dtype_size": (_sz, [_i]),
     "tvb_matmul": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _i64, _vp]),
     "tvb_matmul_algo": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _i64, _vp, _i]),
+    "tvb_matmul_strided": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _i64,
+                                C.POINTER(_i64), C.POINTER(_i64), _vp, _i]),
     "tvb_matmul_plan": (_i, [_i, _i, _i, _i64, _i64, _i64, _i64, _i, C.POINTER(PlanInfo)]),
     "tvb_matmul_host": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _i64]),
     "tvb_fill_splitmix": (_i, [_i, _vp, _i, _u64, _u64, _u64, _i, _vp]),

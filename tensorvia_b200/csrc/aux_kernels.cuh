@@ -55,55 +55,64 @@ __device__ __forceinline__ float elem_to_f32(T x) {
   else return static_cast<float>(x);
 }
 
-// The general split: source elements of type T (fp32, or a type that the product promotes to
-// float: int8/16/32, f16, bf16), one element per thread, destination rows padded to `kp` floats
-// so that TMA can address them.  src is [rows][k] dense, hi/lo are [rows][kp].
+// The split for an operand of any dtype and any strides: element (b, r, c) of a [batch][rows][k]
+// operand lies at src[b*sb + r*sr + c*sc]; hi/lo are [batch*rows][kp] (kp >= k, a multiple of 4
+// so that TMA can address the rows).  Reads are coalesced when sc == 1.
 template <typename T>
 static __global__ void __launch_bounds__(256)
 split_tf32_rows_kernel(const T* __restrict__ src, float* __restrict__ hi, float* __restrict__ lo,
-                       size_t rows, int k, int kp) {
-  const size_t total = rows * static_cast<size_t>(k);
+                       size_t batch, size_t rows, int k, int kp, int64_t sb, int64_t sr, int64_t sc) {
+  const size_t total = batch * rows * static_cast<size_t>(k);
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
   for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-    const size_t r = i / k;
-    const int c = static_cast<int>(i - r * k);
-    const float v = elem_to_f32(src[i]);
+    const size_t rt = i / k;
+    const int c = static_cast<int>(i - rt * k);
+    const size_t b = rt / rows;
+    const size_t r = rt - b * rows;
+    const float v = elem_to_f32(src[static_cast<int64_t>(b) * sb + static_cast<int64_t>(r) * sr + c * sc]);
     const float h = round_tf32(v);
-    hi[r * kp + c] = h;
-    lo[r * kp + c] = round_tf32(v - h);
+    hi[rt * kp + c] = h;
+    lo[rt * kp + c] = round_tf32(v - h);
   }
 }
 
-// Copies dense rows of `width` bytes into rows of `dpitch` bytes (dpitch a multiple of 16, the
-// tail of each row zero-filled): gives 1- and 2-byte operands with an odd row length, or an
-// unaligned base, the 16-byte row pitch TMA needs.  One thread per 16 bytes of destination.
+// Gathers a 1- or 2-byte operand into dense padded rows: dst is [batch][outer][dpitch] elements
+// (dpitch * sizeof(E) a multiple of 16, the tail of each row zero-filled) and element
+// (b, o, i) comes from src[b*sb + o*so + i*si].  Gives operands with an odd row length, an
+// unaligned base or strides TMA cannot encode the 16-byte row pitch it needs.  One thread per
+// 16 bytes of destination; reads are contiguous when si == 1.
+template <typename E>
 static __global__ void __launch_bounds__(256)
-pad_rows_kernel(const unsigned char* __restrict__ src, unsigned char* __restrict__ dst, size_t rows,
-                size_t width, size_t dpitch) {
-  const size_t vec_per_row = dpitch / 16;
-  const size_t total = rows * vec_per_row;
+pad_rows_kernel(const E* __restrict__ src, E* __restrict__ dst, size_t batch, size_t outer, size_t inner,
+                size_t dpitch, int64_t sb, int64_t so, int64_t si) {
+  constexpr int V = 16 / sizeof(E);
+  const size_t vec_per_row = dpitch / V;
+  const size_t total = batch * outer * vec_per_row;
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
   for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-    const size_t r = i / vec_per_row;
-    const size_t x = (i - r * vec_per_row) * 16;
-    const unsigned char* s = src + r * width + x;
-    unsigned char b[16];
+    const size_t rt = i / vec_per_row;
+    const size_t x = (i - rt * vec_per_row) * V;
+    const size_t b = rt / outer;
+    const size_t o = rt - b * outer;
+    const E* s = src + static_cast<int64_t>(b) * sb + static_cast<int64_t>(o) * so;
+    E v[V];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) b[j] = (x + j < width) ? s[j] : static_cast<unsigned char>(0);
-    *reinterpret_cast<uint4*>(dst + r * dpitch + x) = *reinterpret_cast<const uint4*>(b);
+    for (int j = 0; j < V; ++j) v[j] = (x + j < inner) ? s[static_cast<int64_t>(x + j) * si] : E(0);
+    *reinterpret_cast<uint4*>(dst + rt * dpitch + x) = *reinterpret_cast<const uint4*>(v);
   }
 }
 
-// Same split for the B operand, written transposed: src is [batch][K][N], hi and lo are
-// [batch][N][kp] (kp >= K, rows padded to 16 bytes), so the tensor core can read B K-major.  32x32 tiles go through shared
+// The split written transposed: element (z, k, n) of a [batch][K][N] source lies at
+// src[z*sb + k*sk + n] (unit stride along n), hi and lo are [batch][N][kp] (kp >= K, rows padded
+// to 16 bytes), so the tensor core can read the operand K-major.  32x32 tiles go through shared
 // memory: reads are coalesced along N, writes along K.  grid = (ceil(N/32), ceil(K/32), batch).
 template <typename T>
 static __global__ void __launch_bounds__(256)
 split_tf32_transpose_kernel(const T* __restrict__ src, float* __restrict__ hi,
-                            float* __restrict__ lo, int K, int N, int kp) {
+                            float* __restrict__ lo, int K, int N, int kp, int64_t sb, int64_t sk) {
   __shared__ float th[32][33];
   __shared__ float tl[32][33];
-  const size_t boff = static_cast<size_t>(blockIdx.z) * K * N;
+  const T* sbase = src + static_cast<int64_t>(blockIdx.z) * sb;
   const size_t ooff = static_cast<size_t>(blockIdx.z) * N * kp;
   const int n0 = blockIdx.x * 32, k0 = blockIdx.y * 32;
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
@@ -112,7 +121,7 @@ split_tf32_transpose_kernel(const T* __restrict__ src, float* __restrict__ hi,
     const int k = k0 + ty + 8 * j, n = n0 + tx;
     float h = 0.f, l = 0.f;
     if (k < K && n < N) {
-      const float v = elem_to_f32(src[boff + static_cast<size_t>(k) * N + n]);
+      const float v = elem_to_f32(sbase[static_cast<int64_t>(k) * sk + n]);
       h = round_tf32(v);
       l = round_tf32(v - h);
     }

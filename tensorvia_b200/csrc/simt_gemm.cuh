@@ -69,10 +69,16 @@ __device__ __forceinline__ Out from_acc(Acc x) {
   else return static_cast<Out>(x);
 }
 
+// Element strides of the two operands: A(b, m, k) = A[b*a_b + m*a_r + k*a_c], B(b, k, n) likewise.
+// Dense row-major operands have a_b = M*K, a_r = K, a_c = 1 and b_b = K*N, b_r = N, b_c = 1.
+struct SimtStrides {
+  int64_t a_b, a_r, a_c, b_b, b_r, b_c;
+};
+
 template <int DA, int DB>
 __global__ void __launch_bounds__(256)
 simt_gemm_kernel(const void* __restrict__ Av, const void* __restrict__ Bv, void* __restrict__ Cv,
-                 int M, int N, int K) {
+                 int M, int N, int K, const SimtStrides st) {
   using PT = PairTraits<DA, DB>;
   using TA = typename PT::A;
   using TB = typename PT::B;
@@ -84,8 +90,8 @@ simt_gemm_kernel(const void* __restrict__ Av, const void* __restrict__ Bv, void*
   __shared__ Acc Bs[TK][TN];
 
   const size_t batch = blockIdx.z;
-  const TA* A = static_cast<const TA*>(Av) + batch * static_cast<size_t>(M) * K;
-  const TB* B = static_cast<const TB*>(Bv) + batch * static_cast<size_t>(K) * N;
+  const TA* A = static_cast<const TA*>(Av) + static_cast<int64_t>(batch) * st.a_b;
+  const TB* B = static_cast<const TB*>(Bv) + static_cast<int64_t>(batch) * st.b_b;
   Out* C = static_cast<Out*>(Cv) + batch * static_cast<size_t>(M) * N;
 
   const int tx = threadIdx.x & 15;   // 4 columns each
@@ -108,7 +114,7 @@ simt_gemm_kernel(const void* __restrict__ Av, const void* __restrict__ Bv, void*
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int gk = k0 + kk + j;
-        As[kk + j][r] = (gr < M && gk < K) ? to_acc<Acc>(A[static_cast<size_t>(gr) * K + gk]) : Acc(0);
+        As[kk + j][r] = (gr < M && gk < K) ? to_acc<Acc>(A[gr * st.a_r + gk * st.a_c]) : Acc(0);
       }
     }
     // B tile: 16 k x 64 columns; thread t loads k row t/16, 4 consecutive columns
@@ -119,7 +125,7 @@ simt_gemm_kernel(const void* __restrict__ Av, const void* __restrict__ Bv, void*
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int gc = n0 + c + j;
-        Bs[kk][c + j] = (gk < K && gc < N) ? to_acc<Acc>(B[static_cast<size_t>(gk) * N + gc]) : Acc(0);
+        Bs[kk][c + j] = (gk < K && gc < N) ? to_acc<Acc>(B[gk * st.b_r + gc * st.b_c]) : Acc(0);
       }
     }
     __syncthreads();

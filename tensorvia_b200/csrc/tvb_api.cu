@@ -136,10 +136,12 @@ size_t dtype_size(int d) {
 // 3-D map over a [batch, rows, cols] array (cols contiguous, rows `pitch` elements apart) with a
 // [1, box_rows, box_cols] box, 128-byte swizzle and zero fill outside the array.
 int make_map(CUtensorMap* map, CUtensorMapDataType type, size_t es, const void* base, uint64_t cols,
-             uint64_t rows, uint64_t batch, uint64_t pitch, uint32_t box_cols, uint32_t box_rows) {
-  // `pitch` = elements from one row to the next (>= cols; pitch * es a multiple of 16)
+             uint64_t rows, uint64_t batch, uint64_t pitch, uint64_t batch_pitch, uint32_t box_cols,
+             uint32_t box_rows) {
+  // `pitch` = elements from one row to the next, `batch_pitch` = from one batch to the next
+  // (both times es a multiple of 16)
   cuuint64_t dims[3] = {cols, rows, batch};
-  cuuint64_t strides[2] = {pitch * es, rows * pitch * es};
+  cuuint64_t strides[2] = {pitch * es, batch_pitch * es};
   cuuint32_t box[3] = {box_cols, box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = g_encode(map, type, 3, const_cast<void*>(base), dims, strides, box, estr,
@@ -155,21 +157,30 @@ int make_map(CUtensorMap* map, CUtensorMapDataType type, size_t es, const void* 
 // ------------------------------------------------------------------------------------
 // SIMT dispatch: one instantiation per (A dtype, B dtype)
 // ------------------------------------------------------------------------------------
-using SimtLaunch = cudaError_t (*)(const void*, const void*, void*, int, int, int, int, cudaStream_t);
+// One operand as it lies in memory: element (b, r, c) of a [batch, rows, cols] operand is
+// ptr[b*sb + r*sr + c*sc] (strides in elements).
+struct Operand {
+  const void* ptr;
+  int64_t sb, sr, sc;
+};
+inline Operand dense_operand(const void* p, int64_t rows, int64_t cols) { return Operand{p, rows * cols, cols, 1}; }
+
+using SimtLaunch = cudaError_t (*)(const Operand&, const Operand&, void*, int, int, int, int, cudaStream_t);
 
 template <int DA, int DB>
-cudaError_t launch_simt(const void* A, const void* B, void* C, int batch, int M, int N, int K,
+cudaError_t launch_simt(const Operand& a, const Operand& b, void* C, int batch, int M, int N, int K,
                         cudaStream_t s) {
   using PT = PairTraits<DA, DB>;
   const size_t sa = sizeof(typename PT::A), sb = sizeof(typename PT::B), sc = sizeof(typename PT::Out);
+  const SimtStrides st{a.sb, a.sr, a.sc, b.sb, b.sr, b.sc};
   // gridDim.z carries the batch; it is limited to 65535, so long batches go in slices
   for (int b0 = 0; b0 < batch; b0 += 65535) {
     const int nb = (batch - b0 < 65535) ? batch - b0 : 65535;
     dim3 grid((N + 63) / 64, (M + 63) / 64, nb);
     simt_gemm_kernel<DA, DB><<<grid, 256, 0, s>>>(
-        static_cast<const char*>(A) + static_cast<size_t>(b0) * M * K * sa,
-        static_cast<const char*>(B) + static_cast<size_t>(b0) * K * N * sb,
-        static_cast<char*>(C) + static_cast<size_t>(b0) * M * N * sc, M, N, K);
+        static_cast<const char*>(a.ptr) + static_cast<int64_t>(b0) * a.sb * static_cast<int64_t>(sa),
+        static_cast<const char*>(b.ptr) + static_cast<int64_t>(b0) * b.sb * static_cast<int64_t>(sb),
+        static_cast<char*>(C) + static_cast<size_t>(b0) * M * N * sc, M, N, K, st);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
@@ -257,7 +268,7 @@ bool umma_eligible(int dta, int dtb, int64_t batch, int64_t M, int64_t K, int64_
   return true;
 }
 
-template <int OP, int BN, int ST>
+template <int OP, int BN, int ST, int LAYOUT>
 cudaError_t launch_umma_t(const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b0,
                           const CUtensorMap& b1, const UmmaGemmParams& p, int grid, cudaStream_t s) {
   using Cfg = UmmaGemmConfig<OP, BN, ST>;
@@ -265,12 +276,12 @@ cudaError_t launch_umma_t(const CUtensorMap& a0, const CUtensorMap& a1, const CU
   int dev = 0;
   cudaGetDevice(&dev);
   if (!configured[dev].load(std::memory_order_acquire)) {
-    cudaError_t e = cudaFuncSetAttribute(umma_gemm_kernel<OP, BN, ST>,
+    cudaError_t e = cudaFuncSetAttribute(umma_gemm_kernel<OP, BN, ST, LAYOUT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return e;
     configured[dev].store(true, std::memory_order_release);
   }
-  umma_gemm_kernel<OP, BN, ST><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, s>>>(a0, a1, b0, b1, p);
+  umma_gemm_kernel<OP, BN, ST, LAYOUT><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, s>>>(a0, a1, b0, b1, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError();
 }
@@ -318,7 +329,7 @@ inline int pair_capacity(int op, int sm_count) {
   }
 }
 
-template <int OP, int PST>
+template <int OP, int PST, int LAYOUT>
 cudaError_t launch_pair_st(const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b0,
                           const CUtensorMap& b1, const UmmaGemmParams& p, int grid, cudaStream_t s) {
   using Cfg = UmmaPairConfig<OP, PST, kPairKAtoms>;
@@ -326,7 +337,7 @@ cudaError_t launch_pair_st(const CUtensorMap& a0, const CUtensorMap& a1, const C
   int dev = 0;
   cudaGetDevice(&dev);
   if (!configured[dev].load(std::memory_order_acquire)) {
-    cudaError_t e = cudaFuncSetAttribute(umma_gemm_pair_kernel<OP, PST, kPairKAtoms>,
+    cudaError_t e = cudaFuncSetAttribute(umma_gemm_pair_kernel<OP, PST, kPairKAtoms, LAYOUT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return e;
     configured[dev].store(true, std::memory_order_release);
@@ -343,24 +354,49 @@ cudaError_t launch_pair_st(const CUtensorMap& a0, const CUtensorMap& a1, const C
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, umma_gemm_pair_kernel<OP, PST, kPairKAtoms>, a0, a1, b0, b1, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, umma_gemm_pair_kernel<OP, PST, kPairKAtoms, LAYOUT>, a0, a1, b0, b1, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return e != cudaSuccess ? e : cudaGetLastError();
 }
 
+// `layout`: LAYOUT_A_MN | LAYOUT_B_MN bits, how the operands lie in memory (fp32 always 0:
+// its split pass writes both operands K-major)
 template <int OP>
-cudaError_t launch_pair_t(int stages, const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b0,
+cudaError_t launch_pair_t(int layout, const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b0,
                           const CUtensorMap& b1, const UmmaGemmParams& p, int grid, cudaStream_t s) {
-  (void)stages;
-  return launch_pair_st<OP, kPairStages>(a0, a1, b0, b1, p, grid, s);
+  if constexpr (OP == OP_TF32) {
+    return launch_pair_st<OP, kPairStages, 0>(a0, a1, b0, b1, p, grid, s);
+  } else {
+    switch (layout) {
+      case 0: return launch_pair_st<OP, kPairStages, 0>(a0, a1, b0, b1, p, grid, s);
+      case 1: return launch_pair_st<OP, kPairStages, 1>(a0, a1, b0, b1, p, grid, s);
+      case 2: return launch_pair_st<OP, kPairStages, 2>(a0, a1, b0, b1, p, grid, s);
+      default: return launch_pair_st<OP, kPairStages, 3>(a0, a1, b0, b1, p, grid, s);
+    }
+  }
 }
 
-template <int OP>
-cudaError_t launch_umma_op(int block_n, const CUtensorMap& a0, const CUtensorMap& a1,
+template <int OP, int LAYOUT>
+cudaError_t launch_umma_bn(int block_n, const CUtensorMap& a0, const CUtensorMap& a1,
                            const CUtensorMap& b0, const CUtensorMap& b1, const UmmaGemmParams& p,
                            int grid, cudaStream_t s) {
-  if (block_n == 256) return launch_umma_t<OP, 256, 4>(a0, a1, b0, b1, p, grid, s);
-  return launch_umma_t<OP, 128, 6>(a0, a1, b0, b1, p, grid, s);
+  if (block_n == 256) return launch_umma_t<OP, 256, 4, LAYOUT>(a0, a1, b0, b1, p, grid, s);
+  return launch_umma_t<OP, 128, 6, LAYOUT>(a0, a1, b0, b1, p, grid, s);
+}
+template <int OP>
+cudaError_t launch_umma_op(int block_n, int layout, const CUtensorMap& a0, const CUtensorMap& a1,
+                           const CUtensorMap& b0, const CUtensorMap& b1, const UmmaGemmParams& p,
+                           int grid, cudaStream_t s) {
+  if constexpr (OP == OP_TF32) {
+    return launch_umma_bn<OP, 0>(block_n, a0, a1, b0, b1, p, grid, s);
+  } else {
+    switch (layout) {
+      case 0: return launch_umma_bn<OP, 0>(block_n, a0, a1, b0, b1, p, grid, s);
+      case 1: return launch_umma_bn<OP, 1>(block_n, a0, a1, b0, b1, p, grid, s);
+      case 2: return launch_umma_bn<OP, 2>(block_n, a0, a1, b0, b1, p, grid, s);
+      default: return launch_umma_bn<OP, 3>(block_n, a0, a1, b0, b1, p, grid, s);
+    }
+  }
 }
 
 cudaError_t launch_split(Context* c, const void* src, float* hi, float* lo, size_t n, cudaStream_t s) {
@@ -396,38 +432,41 @@ int ensure_workspace(Context* c, size_t bytes, cudaStream_t s) {
   return TVB_OK;
 }
 
+// split of a [batch][rows][k] operand lying at src[b*sb + r*sr + c*sc] into [batch*rows][kp]
 template <typename T>
-cudaError_t launch_split_rows_t(Context* c, const void* src, float* hi, float* lo, size_t rows, int k, int kp,
-                                cudaStream_t s) {
-  size_t blocks = (rows * static_cast<size_t>(k) + 255) / 256;
+cudaError_t launch_split_rows_t(Context* c, const void* src, float* hi, float* lo, size_t batch, size_t rows,
+                                int k, int kp, int64_t sb, int64_t sr, int64_t sc, cudaStream_t s) {
+  size_t blocks = (batch * rows * static_cast<size_t>(k) + 255) / 256;
   const size_t cap = static_cast<size_t>(c->sm_count) * 16;
   if (blocks > cap) blocks = cap;
   if (blocks == 0) blocks = 1;
-  split_tf32_rows_kernel<T><<<static_cast<unsigned>(blocks), 256, 0, s>>>(static_cast<const T*>(src), hi, lo, rows, k, kp);
+  split_tf32_rows_kernel<T><<<static_cast<unsigned>(blocks), 256, 0, s>>>(static_cast<const T*>(src), hi, lo, batch,
+                                                                          rows, k, kp, sb, sr, sc);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError();
 }
-cudaError_t launch_split_rows(Context* c, int dtype, const void* src, float* hi, float* lo, size_t rows, int k,
-                              int kp, cudaStream_t s) {
+cudaError_t launch_split_rows(Context* c, int dtype, const void* src, float* hi, float* lo, size_t batch,
+                              size_t rows, int k, int kp, int64_t sb, int64_t sr, int64_t sc, cudaStream_t s) {
   switch (dtype) {
-    case TVB_INT8: return launch_split_rows_t<int8_t>(c, src, hi, lo, rows, k, kp, s);
-    case TVB_INT16: return launch_split_rows_t<int16_t>(c, src, hi, lo, rows, k, kp, s);
-    case TVB_INT32: return launch_split_rows_t<int32_t>(c, src, hi, lo, rows, k, kp, s);
-    case TVB_BFLOAT16: return launch_split_rows_t<__nv_bfloat16>(c, src, hi, lo, rows, k, kp, s);
-    case TVB_FLOAT16: return launch_split_rows_t<__half>(c, src, hi, lo, rows, k, kp, s);
-    default: return launch_split_rows_t<float>(c, src, hi, lo, rows, k, kp, s);
+    case TVB_INT8: return launch_split_rows_t<int8_t>(c, src, hi, lo, batch, rows, k, kp, sb, sr, sc, s);
+    case TVB_INT16: return launch_split_rows_t<int16_t>(c, src, hi, lo, batch, rows, k, kp, sb, sr, sc, s);
+    case TVB_INT32: return launch_split_rows_t<int32_t>(c, src, hi, lo, batch, rows, k, kp, sb, sr, sc, s);
+    case TVB_BFLOAT16: return launch_split_rows_t<__nv_bfloat16>(c, src, hi, lo, batch, rows, k, kp, sb, sr, sc, s);
+    case TVB_FLOAT16: return launch_split_rows_t<__half>(c, src, hi, lo, batch, rows, k, kp, sb, sr, sc, s);
+    default: return launch_split_rows_t<float>(c, src, hi, lo, batch, rows, k, kp, sb, sr, sc, s);
   }
 }
 template <typename T>
 cudaError_t launch_split_transpose_t(const void* src, float* hi, float* lo, int64_t batch, int K, int N, int kp,
-                                     cudaStream_t s) {
-  // B [batch][K][N] -> hi/lo [batch][N][kp]; gridDim.z carries at most 65535 batches per launch
+                                     int64_t sb, int64_t sk, cudaStream_t s) {
+  // src(z, k, n) = src[z*sb + k*sk + n] -> hi/lo [batch][N][kp]; gridDim.z carries at most 65535
+  // batches per launch
   for (int64_t b0 = 0; b0 < batch; b0 += 65535) {
     const int nbz = static_cast<int>(batch - b0 < 65535 ? batch - b0 : 65535);
     dim3 grid(static_cast<unsigned>((N + 31) / 32), static_cast<unsigned>((K + 31) / 32), nbz);
     split_tf32_transpose_kernel<T><<<grid, 256, 0, s>>>(
-        static_cast<const T*>(src) + static_cast<size_t>(b0) * K * N, hi + static_cast<size_t>(b0) * N * kp,
-        lo + static_cast<size_t>(b0) * N * kp, K, N, kp);
+        static_cast<const T*>(src) + b0 * sb, hi + static_cast<size_t>(b0) * N * kp,
+        lo + static_cast<size_t>(b0) * N * kp, K, N, kp, sb, sk);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
@@ -435,34 +474,52 @@ cudaError_t launch_split_transpose_t(const void* src, float* hi, float* lo, int6
   return cudaSuccess;
 }
 cudaError_t launch_split_transpose(int dtype, const void* src, float* hi, float* lo, int64_t batch, int K, int N,
-                                   int kp, cudaStream_t s) {
+                                   int kp, int64_t sb, int64_t sk, cudaStream_t s) {
   switch (dtype) {
-    case TVB_INT8: return launch_split_transpose_t<int8_t>(src, hi, lo, batch, K, N, kp, s);
-    case TVB_INT16: return launch_split_transpose_t<int16_t>(src, hi, lo, batch, K, N, kp, s);
-    case TVB_INT32: return launch_split_transpose_t<int32_t>(src, hi, lo, batch, K, N, kp, s);
-    case TVB_BFLOAT16: return launch_split_transpose_t<__nv_bfloat16>(src, hi, lo, batch, K, N, kp, s);
-    case TVB_FLOAT16: return launch_split_transpose_t<__half>(src, hi, lo, batch, K, N, kp, s);
-    default: return launch_split_transpose_t<float>(src, hi, lo, batch, K, N, kp, s);
+    case TVB_INT8: return launch_split_transpose_t<int8_t>(src, hi, lo, batch, K, N, kp, sb, sk, s);
+    case TVB_INT16: return launch_split_transpose_t<int16_t>(src, hi, lo, batch, K, N, kp, sb, sk, s);
+    case TVB_INT32: return launch_split_transpose_t<int32_t>(src, hi, lo, batch, K, N, kp, sb, sk, s);
+    case TVB_BFLOAT16: return launch_split_transpose_t<__nv_bfloat16>(src, hi, lo, batch, K, N, kp, sb, sk, s);
+    case TVB_FLOAT16: return launch_split_transpose_t<__half>(src, hi, lo, batch, K, N, kp, sb, sk, s);
+    default: return launch_split_transpose_t<float>(src, hi, lo, batch, K, N, kp, sb, sk, s);
   }
 }
 
-int run_umma(Context* c, const UmmaPlan& plan, int dta, int dtb, const void* A, const void* B, void* C,
+// Splits a [batch][R][K]-like operand (K = the contraction index, stride sk; the other index
+// has `n` values, stride sn) into hi/lo [batch][n][kp]: through the transposing kernel when
+// the operand has unit stride along n, else row by row.
+cudaError_t split_operand(Context* c, int dtype, const void* src, float* hi, float* lo, int64_t batch, int64_t n,
+                          int K, int kp, int64_t sb, int64_t sn, int64_t sk, cudaStream_t s) {
+  const bool unit_k = sk == 1 || K == 1;
+  const bool unit_n = sn == 1 || n == 1;
+  if (!unit_k && unit_n && (K + 31) / 32 <= 65535)
+    return launch_split_transpose(dtype, src, hi, lo, batch, K, static_cast<int>(n), kp, sb, sk, s);
+  return launch_split_rows(c, dtype, src, hi, lo, static_cast<size_t>(batch), static_cast<size_t>(n), K, kp, sb, sn,
+                           sk, s);
+}
+
+int run_umma(Context* c, const UmmaPlan& plan, int dta, int dtb, const Operand& opa, const Operand& opb, void* C,
              int64_t batch, int64_t M, int64_t K, int64_t N, cudaStream_t s) {
   const size_t es = plan.es;
   const uint32_t atom_k = static_cast<uint32_t>(128 / es);  // K elements per 128-byte swizzle atom
-  // K elements per pipeline stage, and the K rows of one MN-major B box
+  // K elements per pipeline stage, and the K rows of one box of an MN-major operand
   const uint32_t bk = plan.pair ? atom_k * kPairKAtoms : atom_k;
   const uint32_t chunk_n = static_cast<uint32_t>(128 / es);
-  const void* a_hi = A;
-  const void* b_hi = B;
-  const void* a_lo = A;
-  const void* b_lo = B;
   auto misaligned = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) != 0; };
   auto round_up = [](size_t v, size_t m) { return (v + m - 1) / m * m; };
   const size_t vec = 16 / es;                                   // elements per 16 bytes
-  uint64_t pitch_a = static_cast<uint64_t>(K);                  // elements between rows of A as the kernel sees it
-  uint64_t pitch_b = static_cast<uint64_t>(N);                  // ... of B ([K,N]; for fp32: of B^T, [N,K])
   const bool c_vec = (N * es) % 16 == 0 && !misaligned(C);
+
+  // What the kernel is given for one operand: where it starts, whether the contraction index
+  // is its contiguous one (K-major) or the other (MN-major), the elements between consecutive
+  // outer indices and between batches.
+  struct Staged {
+    const void* hi;
+    const void* lo;
+    bool mn_major;
+    uint64_t pitch, batch_pitch;
+  };
+  Staged sa{opa.ptr, opa.ptr, false, 0, 0}, sb{opb.ptr, opb.ptr, false, 0, 0};
 
   // Shared-tile plan of the pair kernel (decided here because its scratch shares the block)
   uint32_t sk_rest = 0, sk_kw = 0;
@@ -497,8 +554,9 @@ int run_umma(Context* c, const UmmaPlan& plan, int dta, int dtb, const void* A, 
 
   std::unique_lock<std::mutex> lock(c->mu, std::defer_lock);
   if (plan.op == OP_TF32) {
-    // fp32: split both operands into TF32 hi and lo parts in scratch memory (B transposed on
-    // the way, rows padded to 16 bytes); the 1xTF32 mode uses the hi parts only
+    // fp32: split both operands into TF32 hi and lo parts in scratch memory, both written
+    // K-major ([M][kp] and [N][kp], rows padded to 16 bytes) whatever their strides; the
+    // 1xTF32 mode uses the hi parts only
     lock.lock();
     const size_t kp = round_up(static_cast<size_t>(K), 4);
     const size_t na = static_cast<size_t>(batch) * M * kp, nb = static_cast<size_t>(batch) * N * kp;
@@ -510,69 +568,106 @@ int run_umma(Context* c, const UmmaPlan& plan, int dta, int dtb, const void* A, 
     float* alo = reinterpret_cast<float*>(w + na_b);
     float* bhi = reinterpret_cast<float*>(w + 2 * na_b);
     float* blo = reinterpret_cast<float*>(w + 2 * na_b + nb_b);
-    if (dta == TVB_FLOAT32 && kp == static_cast<size_t>(K) && !misaligned(A)) {
-      TVB_CUDA(launch_split(c, A, ahi, alo, na, s));   // 16-byte vector loads
+    const bool a_dense = opa.sc == 1 && opa.sr == K && (batch == 1 || opa.sb == M * K);
+    if (dta == TVB_FLOAT32 && a_dense && kp == static_cast<size_t>(K) && !misaligned(opa.ptr)) {
+      TVB_CUDA(launch_split(c, opa.ptr, ahi, alo, na, s));   // 16-byte vector loads
     } else {
-      TVB_CUDA(launch_split_rows(c, dta, A, ahi, alo, static_cast<size_t>(batch) * M, static_cast<int>(K),
-                                 static_cast<int>(kp), s));
+      TVB_CUDA(split_operand(c, dta, opa.ptr, ahi, alo, batch, M, static_cast<int>(K), static_cast<int>(kp),
+                             opa.sb, opa.sr, opa.sc, s));
     }
-    // B is split and transposed to [batch][N][kp] in the same pass
-    TVB_CUDA(launch_split_transpose(dtb, B, bhi, blo, batch, static_cast<int>(K), static_cast<int>(N),
-                                    static_cast<int>(kp), s));
-    a_hi = ahi; a_lo = alo; b_hi = bhi; b_lo = blo;
-    pitch_a = kp;
-    pitch_b = kp;
+    // a row-major B is split and transposed to [batch][N][kp] in the same pass; a transposed
+    // view of a dense [N,K] array already lies the way the kernel reads it
+    const bool bt_dense = opb.sr == 1 && opb.sc == K && (batch == 1 || opb.sb == N * K);
+    if (dtb == TVB_FLOAT32 && bt_dense && kp == static_cast<size_t>(K) && !misaligned(opb.ptr)) {
+      TVB_CUDA(launch_split(c, opb.ptr, bhi, blo, nb, s));
+    } else {
+      TVB_CUDA(split_operand(c, dtb, opb.ptr, bhi, blo, batch, N, static_cast<int>(K), static_cast<int>(kp), opb.sb,
+                             opb.sc, opb.sr, s));
+    }
+    sa = Staged{ahi, alo, false, kp, static_cast<uint64_t>(M) * kp};
+    sb = Staged{bhi, blo, false, kp, static_cast<uint64_t>(N) * kp};
   } else {
-    // 1- and 2-byte operands are used in place when their rows start on 16-byte boundaries;
-    // otherwise they are copied once into padded rows
-    const bool pad_a = (K * es) % 16 != 0 || misaligned(A);
-    const bool pad_b = (N * es) % 16 != 0 || misaligned(B);
-    const size_t kpa = round_up(static_cast<size_t>(K), vec), npb = round_up(static_cast<size_t>(N), vec);
-    const size_t pa_bytes = pad_a ? round_up(static_cast<size_t>(batch) * M * kpa * es, 256) : 0;
-    const size_t pb_bytes = pad_b ? round_up(static_cast<size_t>(batch) * K * npb * es, 256) : 0;
-    if (partial_bytes + pa_bytes + pb_bytes > 0) {
+    // 1- and 2-byte operands are used in place, K-major or MN-major as their strides say, when
+    // TMA can address them: unit stride along one index, the other stride and the batch stride
+    // multiples of 16 bytes, a 16-byte aligned base.  Anything else is first gathered into
+    // dense padded rows of scratch memory.
+    struct Prep {
+      bool mn_major, copy;
+      int64_t outer, inner, so, si;   // the copy's (or the map's) outer and inner index
+      size_t dpitch, bytes;
+    };
+    // `mn` = extent of the operand's M or N index, strides s_mn / s_k; natural_mn = the layout
+    // of a dense row-major operand (false for A [M,K], true for B [K,N])
+    auto prepare = [&](const Operand& o, int64_t mn, int64_t s_mn, int64_t s_k, bool natural_mn) {
+      Prep q{};
+      const bool unit_k = s_k == 1 || K == 1, unit_mn = s_mn == 1 || mn == 1;
+      const bool k_major = unit_k && unit_mn ? !natural_mn : (unit_k || (!unit_mn && !natural_mn));
+      q.mn_major = !k_major;
+      q.outer = k_major ? mn : K;
+      q.inner = k_major ? K : mn;
+      q.so = k_major ? s_mn : s_k;
+      q.si = k_major ? s_k : s_mn;
+      const bool unit_inner = k_major ? unit_k : unit_mn;
+      const bool pitch_ok = q.outer == 1 || (q.so >= q.inner && (q.so * static_cast<int64_t>(es)) % 16 == 0);
+      const bool batch_ok = batch == 1 || (o.sb > 0 && (o.sb * static_cast<int64_t>(es)) % 16 == 0);
+      q.copy = !unit_inner || !pitch_ok || !batch_ok || misaligned(o.ptr);
+      q.dpitch = round_up(static_cast<size_t>(q.inner), vec);
+      q.bytes = q.copy ? round_up(static_cast<size_t>(batch) * q.outer * q.dpitch * es, 256) : 0;
+      return q;
+    };
+    const Prep qa = prepare(opa, M, opa.sr, opa.sc, false);
+    const Prep qb = prepare(opb, N, opb.sc, opb.sr, true);
+    if (partial_bytes + qa.bytes + qb.bytes > 0) {
       lock.lock();
-      int rc = ensure_workspace(c, partial_bytes + pa_bytes + pb_bytes, s);
+      int rc = ensure_workspace(c, partial_bytes + qa.bytes + qb.bytes, s);
       if (rc != TVB_OK) return rc;
     }
     char* w = static_cast<char*>(c->ws);
-    auto pad = [&](const void* src, void* dst, size_t rows, size_t width, size_t dpitch) -> cudaError_t {
-      size_t blocks = (rows * (dpitch / 16) + 255) / 256;
+    auto stage_operand = [&](const Operand& o, const Prep& q, void* dst, Staged* out) -> cudaError_t {
+      out->mn_major = q.mn_major;
+      if (!q.copy) {
+        out->hi = out->lo = o.ptr;
+        out->pitch = q.outer == 1 ? round_up(static_cast<size_t>(q.inner), vec) : static_cast<uint64_t>(q.so);
+        out->batch_pitch = batch == 1 ? out->pitch * static_cast<uint64_t>(q.outer) : static_cast<uint64_t>(o.sb);
+        return cudaSuccess;
+      }
+      size_t blocks = (static_cast<size_t>(batch) * q.outer * (q.dpitch / vec) + 255) / 256;
       const size_t cap = static_cast<size_t>(c->sm_count) * 16;
       if (blocks > cap) blocks = cap;
       if (blocks == 0) blocks = 1;
-      pad_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(static_cast<const unsigned char*>(src),
-                                                                   static_cast<unsigned char*>(dst), rows, width, dpitch);
+      if (es == 1)
+        pad_rows_kernel<uint8_t><<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+            static_cast<const uint8_t*>(o.ptr), static_cast<uint8_t*>(dst), static_cast<size_t>(batch),
+            static_cast<size_t>(q.outer), static_cast<size_t>(q.inner), q.dpitch, o.sb, q.so, q.si);
+      else
+        pad_rows_kernel<uint16_t><<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+            static_cast<const uint16_t*>(o.ptr), static_cast<uint16_t*>(dst), static_cast<size_t>(batch),
+            static_cast<size_t>(q.outer), static_cast<size_t>(q.inner), q.dpitch, o.sb, q.so, q.si);
       g_launches.fetch_add(1, std::memory_order_relaxed);
+      out->hi = out->lo = dst;
+      out->pitch = q.dpitch;
+      out->batch_pitch = q.dpitch * static_cast<uint64_t>(q.outer);
       return cudaGetLastError();
     };
-    if (pad_a) {
-      void* dst = w + partial_bytes;
-      TVB_CUDA(pad(A, dst, static_cast<size_t>(batch) * M, static_cast<size_t>(K) * es, kpa * es));
-      a_hi = a_lo = dst;
-      pitch_a = kpa;
-    }
-    if (pad_b) {
-      void* dst = w + partial_bytes + pa_bytes;
-      TVB_CUDA(pad(B, dst, static_cast<size_t>(batch) * K, static_cast<size_t>(N) * es, npb * es));
-      b_hi = b_lo = dst;
-      pitch_b = npb;
-    }
+    TVB_CUDA(stage_operand(opa, qa, w + partial_bytes, &sa));
+    TVB_CUDA(stage_operand(opb, qb, w + partial_bytes + qa.bytes, &sb));
   }
 
+  // A K-major operand is loaded as boxes of 128 B of K x its rows of the tile; an MN-major one
+  // as boxes of 128 B of M (or N) x the stage's rows of K.
   CUtensorMap ma0, ma1, mb0, mb1;
   int rc;
-  if ((rc = make_map(&ma0, plan.tm_type, es, a_hi, K, M, batch, pitch_a, atom_k, 128)) != TVB_OK) return rc;
-  if ((rc = make_map(&ma1, plan.tm_type, es, a_lo, K, M, batch, pitch_a, atom_k, 128)) != TVB_OK) return rc;
-  if (plan.op == OP_TF32) {
-    // B^T[batch][N][K]: boxes of block_n rows x 128 B of K
-    const uint32_t b_rows = plan.pair ? 128u : static_cast<uint32_t>(plan.block_n);  // a pair loads half each
-    if ((rc = make_map(&mb0, plan.tm_type, es, b_hi, K, N, batch, pitch_b, atom_k, b_rows)) != TVB_OK) return rc;
-    if ((rc = make_map(&mb1, plan.tm_type, es, b_lo, K, N, batch, pitch_b, atom_k, b_rows)) != TVB_OK) return rc;
-  } else {
-    if ((rc = make_map(&mb0, plan.tm_type, es, b_hi, N, K, batch, pitch_b, chunk_n, bk)) != TVB_OK) return rc;
-    if ((rc = make_map(&mb1, plan.tm_type, es, b_lo, N, K, batch, pitch_b, chunk_n, bk)) != TVB_OK) return rc;
-  }
+  const uint32_t b_rows = plan.pair ? 128u : static_cast<uint32_t>(plan.block_n);  // a pair loads half of B each
+  auto operand_map = [&](CUtensorMap* m, const void* base, const Staged& st, int64_t mn, uint32_t tile_rows) {
+    if (st.mn_major)
+      return make_map(m, plan.tm_type, es, base, mn, K, batch, st.pitch, st.batch_pitch, chunk_n, bk);
+    return make_map(m, plan.tm_type, es, base, K, mn, batch, st.pitch, st.batch_pitch, atom_k, tile_rows);
+  };
+  if ((rc = operand_map(&ma0, sa.hi, sa, M, 128)) != TVB_OK) return rc;
+  if ((rc = operand_map(&ma1, sa.lo, sa, M, 128)) != TVB_OK) return rc;
+  if ((rc = operand_map(&mb0, sb.hi, sb, N, b_rows)) != TVB_OK) return rc;
+  if ((rc = operand_map(&mb1, sb.lo, sb, N, b_rows)) != TVB_OK) return rc;
+  const int layout = (sa.mn_major ? LAYOUT_A_MN : 0) | (sb.mn_major ? LAYOUT_B_MN : 0);
 
   UmmaGemmParams p;
   p.M = static_cast<int32_t>(M);
@@ -616,17 +711,17 @@ int run_umma(Context* c, const UmmaPlan& plan, int dta, int dtb, const void* A, 
     }
     const int pgrid = 2 * static_cast<int>(p.total_items < pairs ? p.total_items : pairs);
     switch (plan.op) {
-      case OP_F16: e = launch_pair_t<OP_F16>(plan.stages, ma0, ma1, mb0, mb1, p, pgrid, s); break;
-      case OP_BF16: e = launch_pair_t<OP_BF16>(plan.stages, ma0, ma1, mb0, mb1, p, pgrid, s); break;
-      case OP_TF32: e = launch_pair_t<OP_TF32>(plan.stages, ma0, ma1, mb0, mb1, p, pgrid, s); break;
-      default: e = launch_pair_t<OP_I8>(plan.stages, ma0, ma1, mb0, mb1, p, pgrid, s); break;
+      case OP_F16: e = launch_pair_t<OP_F16>(layout, ma0, ma1, mb0, mb1, p, pgrid, s); break;
+      case OP_BF16: e = launch_pair_t<OP_BF16>(layout, ma0, ma1, mb0, mb1, p, pgrid, s); break;
+      case OP_TF32: e = launch_pair_t<OP_TF32>(layout, ma0, ma1, mb0, mb1, p, pgrid, s); break;
+      default: e = launch_pair_t<OP_I8>(layout, ma0, ma1, mb0, mb1, p, pgrid, s); break;
     }
   } else
   switch (plan.op) {
-    case OP_F16: e = launch_umma_op<OP_F16>(plan.block_n, ma0, ma1, mb0, mb1, p, grid, s); break;
-    case OP_BF16: e = launch_umma_op<OP_BF16>(plan.block_n, ma0, ma1, mb0, mb1, p, grid, s); break;
-    case OP_TF32: e = launch_umma_op<OP_TF32>(plan.block_n, ma0, ma1, mb0, mb1, p, grid, s); break;
-    default: e = launch_umma_op<OP_I8>(plan.block_n, ma0, ma1, mb0, mb1, p, grid, s); break;
+    case OP_F16: e = launch_umma_op<OP_F16>(plan.block_n, layout, ma0, ma1, mb0, mb1, p, grid, s); break;
+    case OP_BF16: e = launch_umma_op<OP_BF16>(plan.block_n, layout, ma0, ma1, mb0, mb1, p, grid, s); break;
+    case OP_TF32: e = launch_umma_op<OP_TF32>(plan.block_n, layout, ma0, ma1, mb0, mb1, p, grid, s); break;
+    default: e = launch_umma_op<OP_I8>(plan.block_n, layout, ma0, ma1, mb0, mb1, p, grid, s); break;
   }
   if (e != cudaSuccess) return fail(TVB_ERR_CUDA, "tcgen05 GEMM launch failed: %s", cudaGetErrorString(e));
   if (lock.owns_lock()) {   // this call used the scratch block
@@ -656,13 +751,17 @@ int validate_problem(const void* A, const void* B, const void* C, int dta, int d
   return TVB_OK;
 }
 
-int matmul_impl(int device, const void* A, const void* B, void* C, int dta, int dtb, int dtc,
-                int64_t batch, int64_t M, int64_t K, int64_t N, void* stream, int algo) {
+int matmul_views(int device, const Operand& a, const Operand& b, void* C, int dta, int dtb, int dtc,
+                 int64_t batch, int64_t M, int64_t K, int64_t N, void* stream, int algo) {
+  const void* A = a.ptr;
+  const void* B = b.ptr;
   Context* c = nullptr;
   int rc = get_ctx(device, &c);
   if (rc != TVB_OK) return rc;
   rc = validate_problem(A, B, C, dta, dtb, dtc, batch, M, K, N, true);
   if (rc != TVB_OK) return rc;
+  if (a.sb < 0 || a.sr < 0 || a.sc < 0 || b.sb < 0 || b.sr < 0 || b.sc < 0)
+    return fail(TVB_ERR_INVALID_ARG, "negative strides are not supported");
   if (algo < TVB_ALGO_AUTO || algo > TVB_ALGO_SIMT) return fail(TVB_ERR_INVALID_ARG, "bad algo %d", algo);
   DeviceGuard guard(device);
   cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : c->stream;
@@ -674,14 +773,20 @@ int matmul_impl(int device, const void* A, const void* B, void* C, int dta, int 
                 "the tcgen05 path takes f16 x f16, bf16 x bf16, int8 x int8, fp32 x fp32 and the mixed pairs "
                 "whose result is FLOAT32");
   if (can_umma && algo != TVB_ALGO_SIMT) {
-    rc = run_umma(c, plan, dta, dtb, A, B, C, batch, M, K, N, s);
+    rc = run_umma(c, plan, dta, dtb, a, b, C, batch, M, K, N, s);
     if (rc == TVB_OK || algo == TVB_ALGO_TCGEN05 || rc != TVB_ERR_UNSUPPORTED) return rc;
     // a tensor map the driver would not encode: fall through to the SIMT kernel
   }
-  cudaError_t e = g_simt[dta][dtb](A, B, C, static_cast<int>(batch), static_cast<int>(M),
+  cudaError_t e = g_simt[dta][dtb](a, b, C, static_cast<int>(batch), static_cast<int>(M),
                                    static_cast<int>(N), static_cast<int>(K), s);
   if (e != cudaSuccess) return fail(TVB_ERR_CUDA, "SIMT GEMM launch failed: %s", cudaGetErrorString(e));
   return TVB_OK;
+}
+
+int matmul_impl(int device, const void* A, const void* B, void* C, int dta, int dtb, int dtc,
+                int64_t batch, int64_t M, int64_t K, int64_t N, void* stream, int algo) {
+  return matmul_views(device, dense_operand(A, M, K), dense_operand(B, K, N), C, dta, dtb, dtc, batch, M, K, N,
+                      stream, algo);
 }
 
 template <typename T>
@@ -963,6 +1068,14 @@ int tvb_matmul(int device, const void* A, const void* B, void* C, int dta, int d
 int tvb_matmul_algo(int device, const void* A, const void* B, void* C, int dta, int dtb, int dtc,
                     int64_t batch, int64_t M, int64_t K, int64_t N, void* stream, int algo) {
   return matmul_impl(device, A, B, C, dta, dtb, dtc, batch, M, K, N, stream, algo);
+}
+int tvb_matmul_strided(int device, const void* A, const void* B, void* C, int dta, int dtb, int dtc,
+                       int64_t batch, int64_t M, int64_t K, int64_t N, const int64_t* a_strides,
+                       const int64_t* b_strides, void* stream, int algo) {
+  if (!a_strides || !b_strides) return fail(TVB_ERR_INVALID_ARG, "a_strides and b_strides must not be null");
+  const Operand a{A, a_strides[0], a_strides[1], a_strides[2]};
+  const Operand b{B, b_strides[0], b_strides[1], b_strides[2]};
+  return matmul_views(device, a, b, C, dta, dtb, dtc, batch, M, K, N, stream, algo);
 }
 
 int tvb_matmul_plan(int device, int dta, int dtb, int64_t batch, int64_t M, int64_t K, int64_t N,

@@ -187,7 +187,8 @@ extern "C" int tvb_matmul_f32_static(int device, const void* A, const void* B, v
     dim3 grid(static_cast<unsigned>((N + 31) / 32), static_cast<unsigned>((K + 31) / 32),
               static_cast<unsigned>(batch));
     split_tf32_transpose_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(B), bhi, blo,
-                                                     static_cast<int>(K), static_cast<int>(N), static_cast<int>(K));
+                                                     static_cast<int>(K), static_cast<int>(N), static_cast<int>(K),
+                                                     static_cast<int64_t>(K) * N, static_cast<int64_t>(N));
     TVS_CUDA(cudaGetLastError());
   }
 

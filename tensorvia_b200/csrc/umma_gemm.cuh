@@ -113,6 +113,14 @@ struct UmmaEpilogue {
   static constexpr int WARPS = CHUNKED ? 8 : 4;
 };
 
+// How the two operands lie in memory, as the tensor core is told in the instruction descriptor:
+// bit 0 set = A is MN-major (stored [K, M]: a transposed view of a row-major [K, M] array),
+// bit 1 set = B is MN-major (stored [K, N]: the plain row-major B).  Clear bits mean K-major
+// (A stored [M, K]: plain row-major A; B stored [N, K]: a transposed view).
+enum : int { LAYOUT_A_MN = 1, LAYOUT_B_MN = 2 };
+template <int OP>
+constexpr int default_layout() { return OpTraits<OP>::B_MN_MAJOR ? LAYOUT_B_MN : 0; }
+
 // words of the per-warp staging area of store_block_staged (32 rows x 33: conflict-free both ways)
 constexpr int kStageWords = 32 * 33;
 
@@ -228,7 +236,7 @@ __device__ __forceinline__ void store_block_staged(uint32_t* stage, const uint32
   __syncwarp();
 }
 
-template <int OP, int BLOCK_N, int STAGES>
+template <int OP, int BLOCK_N, int STAGES, int LAYOUT = default_layout<OP>()>
 __global__ void __launch_bounds__(64 + 32 * UmmaEpilogue<OP>::WARPS, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
                  const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
@@ -240,14 +248,17 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
   constexpr int ES = T::ES;
   constexpr int BLOCK_M = Cfg::BLOCK_M;
   constexpr int BK = 128 / ES;                  // K elements per stage
-  constexpr int CHUNK_N = 128 / ES;             // N elements per 128-byte B box
-  constexpr int NCHUNK = BLOCK_N / CHUNK_N;     // B boxes per stage
-  constexpr int CHUNK_BYTES = BK * 128;         // bytes of one B box = LBO of the B descriptor
+  constexpr int CHUNK_N = 128 / ES;             // M or N elements per 128-byte box of an MN-major operand
+  constexpr int NCHUNK = BLOCK_N / CHUNK_N;     // B boxes per stage (MN-major B)
+  constexpr int MCHUNK = BLOCK_M / CHUNK_N;     // A boxes per stage (MN-major A)
+  constexpr int CHUNK_BYTES = BK * 128;         // bytes of one MN-major box = LBO of its descriptor
   constexpr int KSTEPS = 4;                     // 128 B of K per stage / 32 B per MMA
-  constexpr int B_KSTEP_BYTES = (32 / ES) * 128;// K rows of one MMA x 128 B
-  constexpr bool B_MN = T::B_MN_MAJOR != 0;
+  constexpr int B_KSTEP_BYTES = (32 / ES) * 128;// K rows of one MMA x 128 B (MN-major operands)
+  constexpr bool A_MN = (LAYOUT & LAYOUT_A_MN) != 0;
+  constexpr bool B_MN = (LAYOUT & LAYOUT_B_MN) != 0;
+  static_assert(OP != OP_TF32 || LAYOUT == 0, "the TF32 kind reads both operands K-major");
   constexpr uint32_t IDESC =
-      ptx::make_instr_desc(T::D_FMT, T::AB_FMT, 0u, T::B_MN_MAJOR, BLOCK_M, BLOCK_N);
+      ptx::make_instr_desc(T::D_FMT, T::AB_FMT, A_MN ? 1u : 0u, B_MN ? 1u : 0u, BLOCK_M, BLOCK_N);
   static_assert(BLOCK_N % 16 == 0 && BLOCK_N >= 32 && BLOCK_N <= 256, "UMMA N range");
   static_assert((Cfg::TMEM_COLS & (Cfg::TMEM_COLS - 1)) == 0 && Cfg::TMEM_COLS >= 32, "TMEM cols");
   static_assert(BLOCK_N % CHUNK_N == 0, "B tile must be whole 128-byte boxes");
@@ -322,7 +333,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
             const CUtensorMap* ma = (p.passes > 1 && pass == 0) ? &tmA1 : &tmA0;
             const CUtensorMap* mb = (p.passes > 1 && pass == 1) ? &tmB1 : &tmB0;
             ptx::mbar_expect_tx(full_bar(stage), Cfg::STAGE_BYTES);
-            ptx::tma_load_3d(a_smem(stage), ma, full_bar(stage), kb * BK, mt * BLOCK_M, b);
+            if constexpr (A_MN) {
+              // A stored [K, M]: boxes of 128 B of M x BK rows of K, like MN-major B
+#pragma unroll
+              for (int c = 0; c < MCHUNK; ++c)
+                ptx::tma_load_3d(a_smem(stage) + c * CHUNK_BYTES, ma, full_bar(stage),
+                                 mt * BLOCK_M + c * CHUNK_N, kb * BK, b);
+            } else {
+              ptx::tma_load_3d(a_smem(stage), ma, full_bar(stage), kb * BK, mt * BLOCK_M, b);
+            }
             if constexpr (B_MN) {
 #pragma unroll
               for (int c = 0; c < NCHUNK; ++c)
@@ -371,7 +390,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
             const uint32_t b0 = b_smem(stage);
 #pragma unroll
             for (int k = 0; k < KSTEPS; ++k) {
-              const uint64_t adesc = ptx::make_smem_desc(a0 + k * 32, 16, 1024);
+              const uint64_t adesc = A_MN ? ptx::make_smem_desc(a0 + k * B_KSTEP_BYTES, CHUNK_BYTES, 1024)
+                                          : ptx::make_smem_desc(a0 + k * 32, 16, 1024);
               const uint64_t bdesc = B_MN ? ptx::make_smem_desc(b0 + k * B_KSTEP_BYTES, CHUNK_BYTES, 1024)
                                           : ptx::make_smem_desc(b0 + k * 32, 16, 1024);
               ptx::tc_mma<T::MMA>(d_tmem, adesc, bdesc, IDESC, (it > 0 || k > 0) ? 1u : 0u);

@@ -86,7 +86,7 @@ __device__ __forceinline__ PairItem decode_item(uint32_t item, const UmmaGemmPar
 }
 
 // p.m_tiles counts 256-row tiles here; everything else as in UmmaGemmParams.
-template <int OP, int STAGES, int KATOMS>
+template <int OP, int STAGES, int KATOMS, int LAYOUT = default_layout<OP>()>
 __global__ void __launch_bounds__(64 + 32 * UmmaEpilogue<OP>::WARPS, 1)
 umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
                       const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
@@ -101,13 +101,17 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_con
   constexpr int ATOM_K = 128 / ES;               // K elements in one 128-byte swizzle atom
   constexpr int BK = KATOMS * ATOM_K;            // K elements per stage
   constexpr int ATOM_BYTES = 128 * 128;          // 128 rows x 128 B: one K-major tile of one atom
-  constexpr int CHUNK_N = 128 / ES;              // N elements per 128-byte B box (MN-major)
+  constexpr int CHUNK_N = 128 / ES;              // M or N elements per 128-byte box of an MN-major operand
   constexpr int NCHUNK = HALF_B / CHUNK_N;       // B boxes per CTA and stage
+  constexpr int MCHUNK = 128 / CHUNK_N;          // A boxes per CTA and stage (MN-major A)
   constexpr int CHUNK_BYTES = BK * 128;          // one MN-major box: BK k-rows x 128 B
   constexpr int KSTEPS = 4 * KATOMS;
   constexpr int B_KSTEP_BYTES = (32 / ES) * 128;
-  constexpr bool B_MN = T::B_MN_MAJOR != 0;
-  constexpr uint32_t IDESC = ptx::make_instr_desc(T::D_FMT, T::AB_FMT, 0u, T::B_MN_MAJOR, 256, BLOCK_N);
+  constexpr bool A_MN = (LAYOUT & LAYOUT_A_MN) != 0;
+  constexpr bool B_MN = (LAYOUT & LAYOUT_B_MN) != 0;
+  static_assert(OP != OP_TF32 || LAYOUT == 0, "the TF32 kind reads both operands K-major");
+  constexpr uint32_t IDESC =
+      ptx::make_instr_desc(T::D_FMT, T::AB_FMT, A_MN ? 1u : 0u, B_MN ? 1u : 0u, 256, BLOCK_N);
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
@@ -187,10 +191,18 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_con
             const CUtensorMap* ma = (p.passes > 1 && pass == 0) ? &tmA1 : &tmA0;
             const CUtensorMap* mb = (p.passes > 1 && pass == 1) ? &tmB1 : &tmB0;
             if (leader) ptx::mbar_expect_tx(full_bar(stage), 2 * Cfg::STAGE_BYTES);
+            if constexpr (A_MN) {
+              // A stored [K, M]: boxes of 128 B of M x BK rows of K, like MN-major B
 #pragma unroll
-            for (int j = 0; j < KATOMS; ++j)
-              ptx::tma_load_3d_pair(a_smem(stage) + j * ATOM_BYTES, ma, full_bar_leader(stage),
-                                    kb * BK + j * ATOM_K, row0, b);
+              for (int c = 0; c < MCHUNK; ++c)
+                ptx::tma_load_3d_pair(a_smem(stage) + c * CHUNK_BYTES, ma, full_bar_leader(stage),
+                                      row0 + c * CHUNK_N, kb * BK, b);
+            } else {
+#pragma unroll
+              for (int j = 0; j < KATOMS; ++j)
+                ptx::tma_load_3d_pair(a_smem(stage) + j * ATOM_BYTES, ma, full_bar_leader(stage),
+                                      kb * BK + j * ATOM_K, row0, b);
+            }
             if constexpr (B_MN) {
 #pragma unroll
               for (int c = 0; c < NCHUNK; ++c)
@@ -246,7 +258,8 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_con
 #pragma unroll
             for (int k = 0; k < KSTEPS; ++k) {
               const uint32_t koff = (k >> 2) * ATOM_BYTES + (k & 3) * 32;  // atom, then 32 B steps inside it
-              const uint64_t adesc = ptx::make_smem_desc(a0 + koff, 16, 1024);
+              const uint64_t adesc = A_MN ? ptx::make_smem_desc(a0 + k * B_KSTEP_BYTES, CHUNK_BYTES, 1024)
+                                          : ptx::make_smem_desc(a0 + koff, 16, 1024);
               const uint64_t bdesc = B_MN ? ptx::make_smem_desc(b0 + k * B_KSTEP_BYTES, CHUNK_BYTES, 1024)
                                           : ptx::make_smem_desc(b0 + koff, 16, 1024);
               ptx::tc_mma_pair<T::MMA>(d_tmem, adesc, bdesc, IDESC, (it > 0 || k > 0) ? 1u : 0u);

@@ -73,9 +73,10 @@ def matmul(a, b, *, algo: int = ALGO_AUTO, out=None):
     """C = A @ B for torch CUDA tensors (2-D, or 3-D with a leading batch).
 
     Runs on torch's current stream of the tensors' device and does not wait.
-    Inputs must be contiguous: the reference reads its operands as dense row-major
-    whatever their strides (src/backend/cuda/mul.cu:96-121), so a strided view is
-    rejected here instead of being multiplied as if it were dense.
+    Strided views (``b.t()``, ``permute``, slices) are consumed as they lie: the result
+    equals the product of their contiguous copies.  (The reference reads its operands as
+    dense row-major whatever their strides, src/backend/cuda/mul.cu:96-121, so there a view
+    has to go through ``contiguous()`` first, src/tensor.cpp:303-310.)
     """
     import torch
     to_tvb, from_tvb = _torch_maps()
@@ -84,8 +85,7 @@ def matmul(a, b, *, algo: int = ALGO_AUTO, out=None):
     if a.device.type != "cuda":
         raise RuntimeError("tensorvia_b200.matmul needs CUDA tensors; there is no CPU path")
     batch, M, K, N = check_shapes(tuple(a.shape), tuple(b.shape))
-    if not a.is_contiguous() or not b.is_contiguous():
-        raise RuntimeError("matmul operands must be contiguous row-major")
+    strided = not a.is_contiguous() or not b.is_contiguous()
     dta, dtb = to_tvb[a.dtype], to_tvb[b.dtype]
     dtc = compute_type(dta, dtb)
     dev = a.device.index if a.device.index is not None else torch.cuda.current_device()
@@ -99,6 +99,15 @@ def matmul(a, b, *, algo: int = ALGO_AUTO, out=None):
     # torch reports its legacy default stream as handle 0, which the C ABI reads as
     # "the library's own stream"; CUDA's explicit handle for the legacy stream is 1
     stream = torch.cuda.current_stream(a.device).cuda_stream or 1
+    if strided:
+        def strides3(t):
+            st = tuple(t.stride())
+            return (C.c_int64 * 3)(*((0,) + st if t.dim() == 2 else st))
+        if min(a.stride()) < 0 or min(b.stride()) < 0:
+            raise RuntimeError("negative strides are not supported")
+        check(lib.tvb_matmul_strided(dev, a.data_ptr(), b.data_ptr(), out.data_ptr(), dta, dtb, dtc,
+                                     batch, M, K, N, strides3(a), strides3(b), C.c_void_p(stream), algo))
+        return out
     check(lib.tvb_matmul_algo(dev, a.data_ptr(), b.data_ptr(), out.data_ptr(), dta, dtb, dtc,
                               batch, M, K, N, C.c_void_p(stream), algo))
     return out

@@ -86,6 +86,43 @@ class Dev:
         return c, dtc
 
 
+def view_of(storage: np.ndarray, shape, strides, offset: int = 0) -> np.ndarray:
+    """The strided view (strides and offset in elements) of a flat storage array, as numpy sees it."""
+    flat = storage.reshape(-1)
+    item = flat.itemsize
+    return np.lib.stride_tricks.as_strided(flat[offset:], shape=tuple(shape),
+                                           strides=tuple(int(s) * item for s in strides), writeable=False)
+
+
+def matmul_views(dev: Dev, a_store: np.ndarray, a_view, dta: int, b_store: np.ndarray, b_view, dtb: int, algo: int = 0):
+    """C = view(A) @ view(B) through tvb_matmul_strided.  `a_view` / `b_view` are
+    (shape, strides, offset) in elements over the flat storage arrays.  Returns (C, dtype)."""
+    (sha, sta, offa), (shb, stb, offb) = a_view, b_view
+    batch, M, K, N = R.bmkn(tuple(sha), tuple(shb))
+    dtc = dev.lib.tvb_compute_type(dta, dtb)
+    shape_c = (batch, M, N) if len(sha) == 3 else (M, N)
+    pa, pb = dev.upload(a_store), dev.upload(b_store)
+    nbytes = int(np.prod(shape_c)) * R.NP[dtc]().itemsize
+    guard = 256
+    praw = dev.alloc(nbytes + 2 * guard)
+    canary = np.full(nbytes + 2 * guard, 0xA5, dtype=np.uint8)
+    dev.check(dev.lib.tvb_memcpy_h2d(dev.device, praw, canary.ctypes.data, canary.nbytes, None))
+    dev.sync()
+    s3 = lambda st: (C.c_int64 * 3)(*((0,) + tuple(st) if len(st) == 2 else tuple(st)))
+    try:
+        dev.check(dev.lib.tvb_matmul_strided(
+            dev.device, pa + offa * a_store.itemsize, pb + offb * b_store.itemsize, praw + guard, dta, dtb, dtc,
+            batch, M, K, N, s3(sta), s3(stb), None, algo))
+        dev.sync()
+        whole = dev.download(praw, (nbytes + 2 * guard,), R.INT8).view(np.uint8)
+        assert (whole[:guard] == 0xA5).all() and (whole[-guard:] == 0xA5).all(), "write outside C"
+        c = whole[guard:guard + nbytes].copy().view(R.NP[dtc]).reshape(shape_c)
+    finally:
+        for p in (pa, pb, praw):
+            dev.free(p)
+    return c, dtc
+
+
 def assert_matches(c, dtc, expect, dte, tol_f32=1e-5, tol_half=1e-2, tol_f64=1e-12, what=""):
     """Bit-exact for integer results; relative Frobenius error within the tolerance for floats:
     1e-5 for fp32 results, 1e-2 for fp16/bf16 results (fp32 accumulation), 1e-12 for fp64."""

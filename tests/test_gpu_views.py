@@ -1,0 +1,197 @@
+"""Parity of tvb_matmul_strided: operands that are transposed, permuted or sliced views.
+
+What a view means is fixed by the reference's Tensor::t / permute / slice (src/tensor.cpp:217-283)
+and clone_as_contiguous (include/backend/cpu/cpu_tensor.cpp:32-60): element (i, j, ..) of the view
+is storage[offset + i*stride0 + j*stride1 + ..].  The expected product is therefore the oracle's
+product of the views' contiguous copies; bars as everywhere: integers bit-exact, fp32 1e-5,
+fp16/bf16 1e-2 relative Frobenius.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import refcheck as R
+from gpuutil import Dev, assert_matches, matmul_views, view_of
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev(tv):
+    d = Dev(tv)
+    yield d
+    d.free_all()
+
+
+def dense(shape):
+    st, acc = [], 1
+    for n in reversed(shape):
+        st.append(acc)
+        acc *= n
+    return tuple(reversed(st))
+
+
+def transposed_2d(rows, cols):
+    """A [rows, cols] view of a dense [cols, rows] array: what Tensor::t() returns."""
+    return (rows, cols), (1, rows), 0
+
+
+def check(dev, a_store, a_view, dta, b_store, b_view, dtb, algo=0, what=""):
+    c, dtc = matmul_views(dev, a_store, a_view, dta, b_store, b_view, dtb, algo)
+    a = np.ascontiguousarray(view_of(a_store, *a_view))
+    b = np.ascontiguousarray(view_of(b_store, *b_view))
+    exp, dte = R.oracle_matmul(a, dta, b, dtb, "cuda")
+    tol64 = 1e-5 if dtc == R.FLOAT64 and R.INT64 in (dta, dtb) else 1e-12
+    return assert_matches(c, dtc, exp, dte, tol_f64=tol64, what=what)
+
+
+DTYPES_TC = [R.BFLOAT16, R.FLOAT16, R.INT8, R.FLOAT32]
+# (M, K, N): one 128-row tile; CTA pairs with full tiles; pairs with ragged tiles; rows that are
+# not multiples of 16 bytes (the gathering copy)
+SHAPES = [(128, 256, 96), (512, 384, 512), (700, 1040, 528), (300, 1000, 700), (257, 130, 77)]
+
+
+@pytest.mark.parametrize("dt", DTYPES_TC)
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("which", ["b_t", "a_t", "both_t"])
+def test_transposed_views_2d(dev, dt, shape, which):
+    M, K, N = shape
+    dist = 1 if dt == R.INT8 else 0
+    if which in ("a_t", "both_t"):
+        a_store, a_view = R.fill((K, M), dt, 21, dist), transposed_2d(M, K)
+    else:
+        a_store, a_view = R.fill((M, K), dt, 21, dist), ((M, K), dense((M, K)), 0)
+    if which in ("b_t", "both_t"):
+        b_store, b_view = R.fill((N, K), dt, 22, dist), transposed_2d(K, N)
+    else:
+        b_store, b_view = R.fill((K, N), dt, 22, dist), ((K, N), dense((K, N)), 0)
+    check(dev, a_store, a_view, dt, b_store, b_view, dt, what=f"{which} {R.DTYPE_NAMES[dt]} {shape}")
+
+
+@pytest.mark.parametrize("dt", DTYPES_TC)
+def test_batched_permutes(dev, dt):
+    """3-D views: B with its two matrix axes swapped (permute {0,2,1}), A with batch and row axes
+    swapped (permute {1,0,2}: batch stride K, row stride batch*K)."""
+    Bn, M, K, N = 3, 260, 192, 136
+    dist = 1 if dt == R.INT8 else 0
+    a_store = R.fill((M, Bn, K), dt, 31, dist)
+    a_view = ((Bn, M, K), (K, Bn * K, 1), 0)
+    b_store = R.fill((Bn, N, K), dt, 32, dist)
+    b_view = ((Bn, K, N), (N * K, 1, K), 0)
+    check(dev, a_store, a_view, dt, b_store, b_view, dt, what=f"permutes {R.DTYPE_NAMES[dt]}")
+
+
+@pytest.mark.parametrize("dt", DTYPES_TC)
+def test_batch_innermost_permute_is_gathered(dev, dt):
+    """permute {2,0,1} of a [M,K,batch] array: no matrix index has unit stride."""
+    Bn, M, K, N = 2, 140, 96, 130
+    dist = 1 if dt == R.INT8 else 0
+    a_store = R.fill((M, K, Bn), dt, 41, dist)
+    a_view = ((Bn, M, K), (1, K * Bn, Bn), 0)
+    b_store = R.fill((K, N, Bn), dt, 42, dist)
+    b_view = ((Bn, K, N), (1, N * Bn, Bn), 0)
+    check(dev, a_store, a_view, dt, b_store, b_view, dt, what=f"batch-innermost {R.DTYPE_NAMES[dt]}")
+
+
+@pytest.mark.parametrize("dt", DTYPES_TC)
+@pytest.mark.parametrize("off", [(16, 32), (3, 5)])
+def test_sliced_views(dev, dt, off):
+    """Tensor::slice keeps the strides and moves the offset (src/tensor.cpp:226-249): a window of
+    a larger matrix.  (16,32) keeps the window's base on a 16-byte boundary, (3,5) does not."""
+    r0, c0 = off
+    M, K, N = 200, 160, 144
+    dist = 1 if dt == R.INT8 else 0
+    big_a = R.fill((M + 40, K + 64), dt, 51, dist)
+    big_b = R.fill((K + 40, N + 64), dt, 52, dist)
+    a_view = ((M, K), (K + 64, 1), r0 * (K + 64) + c0)
+    b_view = ((K, N), (N + 64, 1), r0 * (N + 64) + c0)
+    check(dev, big_a, a_view, dt, big_b, b_view, dt, what=f"slices {R.DTYPE_NAMES[dt]} {off}")
+
+
+@pytest.mark.parametrize("pair", [(R.INT8, R.FLOAT16), (R.BFLOAT16, R.FLOAT32), (R.INT32, R.INT32),
+                                  (R.FLOAT64, R.FLOAT64), (R.INT64, R.FLOAT32), (R.INT16, R.INT8)])
+def test_views_of_other_dtype_pairs(dev, pair):
+    """Mixed pairs with a FLOAT32 result take the split pass (any strides); the rest the CUDA-core kernel."""
+    dta, dtb = pair
+    M, K, N = 150, 72, 90
+    a_store, a_view = R.fill((K, M), dta, 61, 1 if dta <= R.INT64 else 0), transposed_2d(M, K)
+    b_store, b_view = R.fill((N, K), dtb, 62, 1 if dtb <= R.INT64 else 0), transposed_2d(K, N)
+    check(dev, a_store, a_view, dta, b_store, b_view, dtb, what=f"{pair}")
+
+
+@pytest.mark.parametrize("dt", [R.BFLOAT16, R.INT8])
+def test_views_on_the_cuda_core_kernel(dev, dt):
+    M, K, N = 130, 100, 70
+    dist = 1 if dt == R.INT8 else 0
+    a_store, a_view = R.fill((K, M), dt, 71, dist), transposed_2d(M, K)
+    b_store, b_view = R.fill((N, K), dt, 72, dist), transposed_2d(K, N)
+    check(dev, a_store, a_view, dt, b_store, b_view, dt, algo=2, what="simt views")
+
+
+def test_dense_strides_equal_the_dense_entry_point(dev):
+    """With dense strides the strided entry point runs the very same launch as tvb_matmul."""
+    M, K, N = 512, 256, 512
+    a = R.fill((M, K), R.BFLOAT16, 81)
+    b = R.fill((K, N), R.BFLOAT16, 82)
+    c1, _ = matmul_views(dev, a, ((M, K), dense((M, K)), 0), R.BFLOAT16, b, ((K, N), dense((K, N)), 0), R.BFLOAT16)
+    c2, _ = dev.matmul(a, R.BFLOAT16, b, R.BFLOAT16)
+    assert c1.tobytes() == c2.tobytes()
+
+
+def test_transposed_views_equal_their_copies_bitwise_int8(dev):
+    M, K, N = 384, 512, 320
+    bt = R.fill((N, K), R.INT8, 91, 1)
+    a = R.fill((M, K), R.INT8, 92, 1)
+    c1, _ = matmul_views(dev, a, ((M, K), dense((M, K)), 0), R.INT8, bt, transposed_2d(K, N), R.INT8)
+    c2, _ = dev.matmul(a, R.INT8, np.ascontiguousarray(bt.T), R.INT8)
+    assert c1.tobytes() == c2.tobytes()
+
+
+@pytest.mark.parametrize("dt", [R.BFLOAT16, R.FLOAT16, R.INT8])
+def test_aligned_transposed_views_are_read_in_place(dev, dt):
+    """One launch: the GEMM itself, no gathering copy (fp32 always has its split launches)."""
+    M, K, N = 512, 384, 512
+    dist = 1 if dt == R.INT8 else 0
+    a_store, b_store = R.fill((K, M), dt, 95, dist), R.fill((N, K), dt, 96, dist)
+    before = dev.lib.tvb_kernel_launches()
+    matmul_views(dev, a_store, transposed_2d(M, K), dt, b_store, transposed_2d(K, N), dt)
+    assert dev.lib.tvb_kernel_launches() - before == 1
+    # an odd pitch cannot be addressed by TMA: one copy per operand, then the GEMM
+    a_store, b_store = R.fill((K, M + 1), dt, 95, dist), R.fill((N, K + 1), dt, 96, dist)
+    before = dev.lib.tvb_kernel_launches()
+    matmul_views(dev, a_store, ((M, K), (1, M + 1), 0), dt, b_store, ((K, N), (1, K + 1), 0), dt)
+    assert dev.lib.tvb_kernel_launches() - before == 3
+
+
+def test_negative_strides_are_refused(dev):
+    lib = dev.lib
+    p = dev.alloc(4096)
+    try:
+        sa = (C.c_int64 * 3)(0, 8, -1)
+        sb = (C.c_int64 * 3)(0, 8, 1)
+        rc = lib.tvb_matmul_strided(0, p, p, p, R.FLOAT32, R.FLOAT32, R.FLOAT32, 1, 8, 8, 8, sa, sb, None, 0)
+        assert rc == 1  # TVB_ERR_INVALID_ARG
+        assert b"negative" in lib.tvb_last_error_string()
+        assert lib.tvb_matmul_strided(0, p, p, p, R.FLOAT32, R.FLOAT32, R.FLOAT32, 1, 8, 8, 8, None, sb, None, 0) == 1
+    finally:
+        dev.free(p)
+
+
+def test_torch_views_through_ops(tv):
+    torch = pytest.importorskip("torch")
+    ops = tv.ops
+    g = torch.Generator(device="cuda").manual_seed(5)
+    w = (torch.rand((320, 256), device="cuda", generator=g) * 2 - 1).to(torch.bfloat16)   # [N, K]
+    x = (torch.rand((200, 256), device="cuda", generator=g) * 2 - 1).to(torch.bfloat16)   # [M, K]
+    got = ops.matmul(x, w.t())
+    want = ops.matmul(x, w.t().contiguous())
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+    xb = (torch.rand((4, 96, 130), device="cuda", generator=g) * 2 - 1)                    # fp32 [B, K, M]
+    yb = (torch.rand((4, 96, 64), device="cuda", generator=g) * 2 - 1)
+    got = ops.matmul(xb.permute(0, 2, 1), yb)
+    want = ops.matmul(xb.permute(0, 2, 1).contiguous(), yb)
+    torch.cuda.synchronize()
+    err = (got.double() - want.double()).norm() / want.double().norm()
+    assert err.item() <= 1e-5
