@@ -15,6 +15,7 @@
 #include <cstring>
 #include <exception>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "ops.h"
@@ -77,6 +78,118 @@ int tvref_mul(const void* a, int dtype_a, int rank_a, const int64_t* dims_a, con
     g_msg = "unknown exception";
     return 1;
   }
+}
+
+// ---- layout operations either side of the matmul ------------------------------------------
+// Each returns 0 on success, 1 if the reference threw, 2 if `out` was too small; the result's
+// dims go to out_dims (room for `rank` entries).
+}  // extern "C"
+namespace {
+int emit(const Tensor& t, void* out, uint64_t out_bytes, int64_t* out_dims) {
+  const std::vector<int64_t> s = t.shape();
+  if (out_dims)
+    for (size_t i = 0; i < s.size(); ++i) out_dims[i] = s[i];
+  const uint64_t bytes = static_cast<uint64_t>(t.numel()) * via::calc_dtype_size(t.dtype());
+  if (bytes > out_bytes) {
+    g_msg = "result buffer too small";
+    return 2;
+  }
+  std::memcpy(out, t.data(), bytes);
+  return 0;
+}
+template <typename F>
+int guarded(F&& f) {
+  try {
+    return f();
+  } catch (const std::exception& e) {
+    g_msg = e.what();
+    return 1;
+  } catch (...) {
+    g_msg = "unknown exception";
+    return 1;
+  }
+}
+}  // namespace
+extern "C" {
+
+// Tensor::permute(perm).contiguous()  (src/tensor.cpp:250-283, 303-310)
+int tvref_permute_contiguous(const void* data, int dtype, int rank, const int64_t* dims, const int64_t* perm,
+                             void* out, uint64_t out_bytes, int64_t* out_dims) {
+  return guarded([&] {
+    Tensor t(const_cast<void*>(data), shape_of(rank, dims), static_cast<via::DataType>(dtype), via::Device::CPU);
+    Tensor v = std::as_const(t).permute(std::vector<int64_t>(perm, perm + rank));
+    Tensor c = std::as_const(v).contiguous();
+    return emit(c, out, out_bytes, out_dims);
+  });
+}
+
+// Tensor::slice(ranges).contiguous()  (src/tensor.cpp:226-249, 303-310)
+int tvref_slice_view_contiguous(const void* data, int dtype, int rank, const int64_t* dims, int nranges,
+                                const int64_t* begin, const int64_t* end, void* out, uint64_t out_bytes,
+                                int64_t* out_dims) {
+  return guarded([&] {
+    Tensor t(const_cast<void*>(data), shape_of(rank, dims), static_cast<via::DataType>(dtype), via::Device::CPU);
+    std::vector<std::pair<int64_t, int64_t>> r;
+    for (int i = 0; i < nranges; ++i) r.emplace_back(begin[i], end[i]);
+    Tensor v = std::as_const(t).slice(r);
+    Tensor c = std::as_const(v).contiguous();
+    return emit(c, out, out_bytes, out_dims);
+  });
+}
+
+// ops::Slice  (src/ops.cpp:158-190)
+int tvref_slice(const void* data, int dtype, int rank, const int64_t* dims, int nranges, const int64_t* begin,
+                const int64_t* end, void* out, uint64_t out_bytes, int64_t* out_dims) {
+  return guarded([&] {
+    Tensor t(const_cast<void*>(data), shape_of(rank, dims), static_cast<via::DataType>(dtype), via::Device::CPU);
+    std::vector<std::pair<int64_t, int64_t>> r;
+    for (int i = 0; i < nranges; ++i) r.emplace_back(begin[i], end[i]);
+    Tensor c = ops::Slice(t, r);
+    return emit(c, out, out_bytes, out_dims);
+  });
+}
+
+// ops::Concat  (src/ops.cpp:1301-1333); dims_flat holds count * rank extents
+int tvref_concat(int count, const void* const* datas, int dtype, int rank, const int64_t* dims_flat, int dim,
+                 void* out, uint64_t out_bytes, int64_t* out_dims) {
+  return guarded([&] {
+    std::vector<Tensor> ts;
+    ts.reserve(count);
+    for (int i = 0; i < count; ++i)
+      ts.emplace_back(const_cast<void*>(datas[i]), shape_of(rank, dims_flat + i * rank),
+                      static_cast<via::DataType>(dtype), via::Device::CPU);
+    Tensor c = ops::Concat(ts, dim);
+    return emit(c, out, out_bytes, out_dims);
+  });
+}
+
+// ops::Transpose on a 2-D tensor, in place  (src/ops.cpp:1334-1350)
+int tvref_transpose2d(const void* data, int dtype, int64_t rows, int64_t cols, void* out, uint64_t out_bytes,
+                      int64_t* out_dims) {
+  return guarded([&] {
+    Tensor t(const_cast<void*>(data), std::vector<int64_t>{rows, cols}, static_cast<via::DataType>(dtype),
+             via::Device::CPU);
+    ops::Transpose(t);
+    return emit(t, out, out_bytes, out_dims);
+  });
+}
+
+// ops::Mul(a.t()-style views made contiguous): a and b are given with their STORED shapes and a
+// permutation each; the product is Mul(a.permute(pa).contiguous(), b.permute(pb).contiguous()).
+int tvref_mul_permuted(const void* a, int dtype_a, int rank, const int64_t* dims_a, const int64_t* perm_a,
+                       const void* b, int dtype_b, const int64_t* dims_b, const int64_t* perm_b, void* c,
+                       uint64_t c_bytes, int* dtype_c, int64_t* dims_c) {
+  return guarded([&] {
+    Tensor ta(const_cast<void*>(a), shape_of(rank, dims_a), static_cast<via::DataType>(dtype_a), via::Device::CPU);
+    Tensor tb(const_cast<void*>(b), shape_of(rank, dims_b), static_cast<via::DataType>(dtype_b), via::Device::CPU);
+    Tensor va = std::as_const(ta).permute(std::vector<int64_t>(perm_a, perm_a + rank));
+    Tensor vb = std::as_const(tb).permute(std::vector<int64_t>(perm_b, perm_b + rank));
+    Tensor ca = std::as_const(va).contiguous();
+    Tensor cb = std::as_const(vb).contiguous();
+    Tensor tc = ops::Mul(ca, cb);
+    if (dtype_c) *dtype_c = static_cast<int>(tc.dtype());
+    return emit(tc, c, c_bytes, dims_c);
+  });
 }
 
 }  // extern "C"

@@ -11,6 +11,9 @@ so the pin is the reference's implementation run here on seeded inputs:
   golden_tiled.npz    the large-output path (mul_kernel_tiled<64>, mul.cpp:27-85): sampled rows
                       and a SHA-256 of the whole result
   golden_configs.npz  sampled rows of the five benchmark configurations at FULL size
+  golden_layout.npz   the layout operations either side of the matmul: permute().contiguous(),
+                      ops::Slice, slice().contiguous(), ops::Concat, ops::Transpose, and ops::Mul of
+                      permuted views made contiguous
   golden_meta.json    compute_type table, the messages ops::Mul throws for bad shapes
                       (src/ops.cpp:540-556), thread count, sizes
 
@@ -164,9 +167,41 @@ SHAPE_CASES = [((2, 3), (4, 5)), ((2, 3), (3,)), ((2, 3, 4), (3, 4, 5)), ((2, 3,
                ((2, 3), (3, 4)), ((2, 3, 4, 5), (2, 3, 5, 4)), ((2, 3, 4), (2, 4, 6)), ((2, 3), (2, 3, 4))]
 
 
+# ---- layout operations: views made contiguous, slices, concatenation, views multiplied ----------
+from layout_cases import CONCAT_CASES, LAYOUT_DTYPES, MUL_VIEW_CASES, PERMUTE_CASES, SLICE_CASES, pins_view_route  # noqa: E402
+
+
+def layout():
+    out = {}
+    for dt in LAYOUT_DTYPES:
+        for i, (shape, perm) in enumerate(PERMUTE_CASES):
+            out[f"permute_{dt}_{i}"] = R.ref_permute_contiguous(R.fill(shape, dt, 500 + i, F(dt)), dt, perm)
+        for i, (shape, b, e) in enumerate(SLICE_CASES):
+            x = R.fill(shape, dt, 600 + i, F(dt))
+            out[f"slice_{dt}_{i}"] = R.ref_slice(x, dt, b, e)
+            # the view route is pinned only where the view is not a leading-dimension slice:
+            # there the reference drops the offset (see oracle/layout_oracle.c)
+            if pins_view_route(shape, b, e):
+                out[f"sliceview_{dt}_{i}"] = R.ref_slice(x, dt, b, e, view=True)
+        for i, (shapes, dim) in enumerate(CONCAT_CASES):
+            parts = [R.fill(sh, dt, 700 + 10 * i + j, F(dt)) for j, sh in enumerate(shapes)]
+            out[f"concat_{dt}_{i}"] = R.ref_concat(parts, dt, dim)
+        out[f"transpose_{dt}"] = R.ref_transpose2d(R.fill((37, 66), dt, 800, F(dt)), dt)
+    for i, (dt, sa, pa, sb, pb) in enumerate(MUL_VIEW_CASES):
+        c, dtc = R.ref_mul_permuted(R.fill(sa, dt, 900 + i, F(dt)), dt, pa, R.fill(sb, dt, 950 + i, F(dt)), dt, pb)
+        out[f"mulview_{i}"] = c
+        out[f"mulview_{i}_dt"] = np.int32(dtc)
+    np.savez_compressed(HERE / "golden_layout.npz", **out)
+
+
 def main():
     assert R.have_ref(), "build the reference first: make -C oracle ref"
+    if "--layout-only" in sys.argv:
+        layout()
+        print("golden_layout.npz written to", HERE)
+        return
     small()
+    layout()
     meta = {"tiled": tiled(), "configs": configs()}
     meta["compute_type"] = [[int(R.ref().tvref_compute_type(a, b)) for b in range(8)] for a in range(8)]
     meta["shape_messages"] = [{"a": list(sa), "b": list(sb), "message": R.ref_validate(sa, sb)} for sa, sb in SHAPE_CASES]

@@ -34,7 +34,8 @@ SEED_BASE = 0x5EED0000
 
 
 def build_oracle() -> Path:
-    if not ORACLE_LIB.exists() or ORACLE_LIB.stat().st_mtime < (ORACLE_DIR / "matmul_oracle.c").stat().st_mtime:
+    newest = max((ORACLE_DIR / f).stat().st_mtime for f in ("matmul_oracle.c", "layout_oracle.c"))
+    if not ORACLE_LIB.exists() or ORACLE_LIB.stat().st_mtime < newest:
         subprocess.run(["make", "-C", str(ORACLE_DIR), "oracle"], check=True, capture_output=True)
     return ORACLE_LIB
 
@@ -95,6 +96,13 @@ def ref() -> C.CDLL:
         lib.tvref_compute_type.restype = C.c_int
         lib.tvref_compute_type.argtypes = [C.c_int, C.c_int]
         lib.tvref_threads.restype = C.c_int
+        vp, u64, i = C.c_void_p, C.c_uint64, C.c_int
+        lib.tvref_permute_contiguous.argtypes = [vp, i, i, i64p, i64p, vp, u64, i64p]
+        lib.tvref_slice_view_contiguous.argtypes = [vp, i, i, i64p, i, i64p, i64p, vp, u64, i64p]
+        lib.tvref_slice.argtypes = [vp, i, i, i64p, i, i64p, i64p, vp, u64, i64p]
+        lib.tvref_concat.argtypes = [i, C.POINTER(vp), i, i, i64p, i, vp, u64, i64p]
+        lib.tvref_transpose2d.argtypes = [vp, i, C.c_int64, C.c_int64, vp, u64, i64p]
+        lib.tvref_mul_permuted.argtypes = [vp, i, i, i64p, i64p, vp, i, i64p, i64p, vp, u64, C.POINTER(i), i64p]
         _ref = lib
     return _ref
 
@@ -230,3 +238,129 @@ def cuda_expected_from_cpu(c: np.ndarray, dtc_cpu: int, dta: int, dtb: int) -> t
 
 def sha(arr: np.ndarray) -> str:
     return hashlib.sha256(np.ascontiguousarray(arr).tobytes()).hexdigest()
+
+
+# ---- layout operations (views made contiguous, slices, concatenation) ---------------------------
+def _i64(vals):
+    return (C.c_int64 * len(vals))(*[int(v) for v in vals])
+
+
+def dense_strides(shape):
+    st, acc = [], 1
+    for n in reversed(shape):
+        st.append(acc)
+        acc *= int(n)
+    return tuple(reversed(st))
+
+
+def oracle_repack(storage: np.ndarray, shape, strides, offset: int = 0) -> np.ndarray:
+    """clone_as_contiguous of the view (shape, strides, offset in elements) of `storage`."""
+    storage = np.ascontiguousarray(storage)
+    out = np.empty(tuple(shape), dtype=storage.dtype)
+    rc = oracle().tvo_repack(C.c_void_p(storage.ctypes.data), C.c_void_p(out.ctypes.data), C.c_size_t(storage.itemsize),
+                             len(shape), _i64(shape), _i64(strides), C.c_int64(offset))
+    assert rc == 0
+    return out
+
+
+def oracle_slice(x: np.ndarray, begin, end) -> np.ndarray:
+    x = np.ascontiguousarray(x)
+    shape = [e - b for b, e in zip(begin, end)] + list(x.shape[len(begin):])
+    out = np.empty(shape, dtype=x.dtype)
+    rc = oracle().tvo_slice(C.c_void_p(x.ctypes.data), C.c_void_p(out.ctypes.data), C.c_size_t(x.itemsize), x.ndim,
+                            _i64(x.shape), len(begin), _i64(begin), _i64(end))
+    assert rc == 0
+    return out
+
+
+def oracle_concat(parts, dim: int) -> np.ndarray:
+    parts = [np.ascontiguousarray(p) for p in parts]
+    shape = list(parts[0].shape)
+    sizes = [p.shape[dim] for p in parts]
+    shape[dim] = sum(sizes)
+    out = np.empty(shape, dtype=parts[0].dtype)
+    ptrs = (C.c_void_p * len(parts))(*[p.ctypes.data for p in parts])
+    rc = oracle().tvo_concat(len(parts), ptrs, C.c_void_p(out.ctypes.data), C.c_size_t(out.itemsize), out.ndim,
+                             _i64(parts[0].shape), _i64(sizes), dim)
+    assert rc == 0
+    return out
+
+
+def oracle_transpose(x: np.ndarray) -> np.ndarray:
+    x = np.ascontiguousarray(x)
+    out = np.empty((x.shape[1], x.shape[0]), dtype=x.dtype)
+    rc = oracle().tvo_transpose(C.c_void_p(x.ctypes.data), C.c_void_p(out.ctypes.data), C.c_size_t(x.itemsize),
+                                C.c_int64(x.shape[0]), C.c_int64(x.shape[1]))
+    assert rc == 0
+    return out
+
+
+def _ref_out(rc, lib, out, dims, rank):
+    if rc != 0:
+        raise RuntimeError(lib.tvref_last_error().decode())
+    shape = tuple(dims[i] for i in range(rank))
+    return out[: int(np.prod(shape))].reshape(shape)
+
+
+def ref_permute_contiguous(x: np.ndarray, dtype: int, perm) -> np.ndarray:
+    lib = ref()
+    x = np.ascontiguousarray(x)
+    out = np.empty(x.size, dtype=x.dtype)
+    dims = _i64([0] * x.ndim)
+    rc = lib.tvref_permute_contiguous(x.ctypes.data, dtype, x.ndim, _i64(x.shape), _i64(perm), out.ctypes.data,
+                                      out.nbytes, dims)
+    return _ref_out(rc, lib, out, dims, x.ndim)
+
+
+def ref_slice(x: np.ndarray, dtype: int, begin, end, view: bool = False) -> np.ndarray:
+    """ops::Slice (view=False) or Tensor::slice(...).contiguous() (view=True)."""
+    lib = ref()
+    x = np.ascontiguousarray(x)
+    out = np.empty(x.size, dtype=x.dtype)
+    dims = _i64([0] * x.ndim)
+    fn = lib.tvref_slice_view_contiguous if view else lib.tvref_slice
+    rc = fn(x.ctypes.data, dtype, x.ndim, _i64(x.shape), len(begin), _i64(begin), _i64(end), out.ctypes.data,
+            out.nbytes, dims)
+    return _ref_out(rc, lib, out, dims, x.ndim)
+
+
+def ref_concat(parts, dtype: int, dim: int) -> np.ndarray:
+    lib = ref()
+    parts = [np.ascontiguousarray(p) for p in parts]
+    rank = parts[0].ndim
+    out = np.empty(sum(p.size for p in parts), dtype=parts[0].dtype)
+    dims = _i64([0] * rank)
+    ptrs = (C.c_void_p * len(parts))(*[p.ctypes.data for p in parts])
+    flat = _i64([d for p in parts for d in p.shape])
+    rc = lib.tvref_concat(len(parts), ptrs, dtype, rank, flat, dim, out.ctypes.data, out.nbytes, dims)
+    return _ref_out(rc, lib, out, dims, rank)
+
+
+def ref_transpose2d(x: np.ndarray, dtype: int) -> np.ndarray:
+    lib = ref()
+    x = np.ascontiguousarray(x)
+    out = np.empty(x.size, dtype=x.dtype)
+    dims = _i64([0, 0])
+    rc = lib.tvref_transpose2d(x.ctypes.data, dtype, x.shape[0], x.shape[1], out.ctypes.data, out.nbytes, dims)
+    return _ref_out(rc, lib, out, dims, 2)
+
+
+def ref_mul_permuted(a: np.ndarray, dta: int, perm_a, b: np.ndarray, dtb: int, perm_b):
+    """ops::Mul(a.permute(perm_a).contiguous(), b.permute(perm_b).contiguous()) in the reference."""
+    lib = ref()
+    a, b = np.ascontiguousarray(a), np.ascontiguousarray(b)
+    dtc = lib.tvref_compute_type(dta, dtb)
+    if dta in (BFLOAT16, FLOAT16) and dtb in (BFLOAT16, FLOAT16) and dta == dtb:
+        dtc = FLOAT32   # the CPU backend multiplies halves as fp32 and returns FLOAT32 (mul.cpp:110-113)
+    sa = [a.shape[p] for p in perm_a]
+    sb = [b.shape[p] for p in perm_b]
+    shape_c = sa[:-1] + [sb[-1]]
+    out = np.empty(int(np.prod(shape_c)), dtype=np.float64)   # room for any dtype
+    dims = _i64([0] * a.ndim)
+    got = C.c_int(-1)
+    rc = lib.tvref_mul_permuted(a.ctypes.data, dta, a.ndim, _i64(a.shape), _i64(perm_a), b.ctypes.data, dtb,
+                                _i64(b.shape), _i64(perm_b), out.ctypes.data, out.nbytes, C.byref(got), dims)
+    if rc != 0:
+        raise RuntimeError(lib.tvref_last_error().decode())
+    n = int(np.prod(shape_c))
+    return out.view(np.uint8)[: n * NP[got.value]().itemsize].view(NP[got.value]).reshape(shape_c).copy(), got.value
