@@ -116,6 +116,39 @@ int tvb_memcpy_h2d(int device, void* dst, const void* src, size_t bytes, void* s
 int tvb_memcpy_d2h(int device, void* dst, const void* src, size_t bytes, void* stream);
 int tvb_memcpy_d2d(int device, void* dst, const void* src, size_t bytes, void* stream);
 
+/* ---- layout operations either side of the matmul -------------------------------------
+ * Byte movers, each one pass at memory speed: every element is read once and written once.
+ * All take dense device buffers unless said otherwise, extents and strides in ELEMENTS of
+ * `dtype`, at most 8 dimensions, and run on `stream` (NULL = the context's stream) without
+ * waiting. */
+/* A strided view made contiguous: dst[row-major index of (i0, i1, ..)] =
+ * src[i0*strides[0] + i1*strides[1] + ..]; src points at the view's first element (storage
+ * base + Metadata::offset).  Replaces TensorImpl::clone_as_contiguous as the CUDA tensor does
+ * it (include/backend/cuda/cuda_tensor.cpp:52-56 -> RepackImpl, src/backend/cuda/repack.cu:
+ * 5-54), which is what Tensor::contiguous(), to_contiguous() and clone() apply to the views
+ * made by t(), permute() and slice() (src/tensor.cpp:217-310).  Unlike the reference, the
+ * offset of a leading-dimension slice view is honoured (there is_contiguous() passes and the
+ * copy starts at the storage base). */
+int tvb_repack(int device, const void* src, void* dst, int dtype, int ndim,
+               const int64_t* shape, const int64_t* strides, void* stream);
+/* ops::Slice (src/ops.cpp:158-190 -> SliceImpl<Device::CUDA>::execute,
+ * src/backend/cuda/slice.cu:7-114): dst = the window [begin[i], end[i]) of the first `nranges`
+ * dimensions of a dense src of `shape`, the other dimensions whole.  A window of leading rows
+ * is one device-to-device copy.  TVB_ERR_SHAPE for a range outside the tensor or empty. */
+int tvb_slice(int device, const void* src, void* dst, int dtype, int ndim, const int64_t* shape,
+              int nranges, const int64_t* begin, const int64_t* end, void* stream);
+/* ops::Concat (src/ops.cpp:1301-1333 -> ConcatImpl<Device::CUDA>::execute,
+ * src/backend/cuda/concat.cu:8-158): `count` dense tensors that agree in every dimension but
+ * `dim`, where tensor t has dim_sizes[t] entries (`shape` gives the common extents, its entry
+ * at `dim` is ignored), joined along `dim` into dst.  Along dim 0 each part is one
+ * device-to-device copy: the gather step of row-sharded results. */
+int tvb_concat(int device, int count, const void* const* srcs, void* dst, int dtype, int ndim,
+               const int64_t* shape, const int64_t* dim_sizes, int dim, void* stream);
+/* ops::Transpose of a 2-D tensor (src/ops.cpp:1334-1353 -> TransposeImpl<Device::CUDA>::execute,
+ * src/backend/cuda/transpose.cu:8-51), out of place: dst[cols, rows] = src[rows, cols]^T. */
+int tvb_transpose2d(int device, const void* src, void* dst, int dtype, int64_t rows, int64_t cols,
+                    void* stream);
+
 /* ---- dtype rules -----------------------------------------------------------------*/
 /* via::compute_type (include/core/type_traits.h:270-287); -1 for a bad dtype. */
 int tvb_compute_type(int dtype_a, int dtype_b);

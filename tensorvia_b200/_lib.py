@@ -69,6 +69,10 @@ SIGNATURES = {
     "tvb_matmul_algo": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _i64, _vp, _i]),
     "tvb_matmul_strided": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _i64,
                                 C.POINTER(_i64), C.POINTER(_i64), _vp, _i]),
+    "tvb_repack": (_i, [_i, _vp, _vp, _i, _i, C.POINTER(_i64), C.POINTER(_i64), _vp]),
+    "tvb_slice": (_i, [_i, _vp, _vp, _i, _i, C.POINTER(_i64), _i, C.POINTER(_i64), C.POINTER(_i64), _vp]),
+    "tvb_concat": (_i, [_i, _i, C.POINTER(_vp), _vp, _i, _i, C.POINTER(_i64), C.POINTER(_i64), _i, _vp]),
+    "tvb_transpose2d": (_i, [_i, _vp, _vp, _i, _i64, _i64, _vp]),
     "tvb_matmul_plan": (_i, [_i, _i, _i, _i64, _i64, _i64, _i64, _i, C.POINTER(PlanInfo)]),
     "tvb_matmul_host": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _i64]),
     "tvb_fill_splitmix": (_i, [_i, _vp, _i, _u64, _u64, _u64, _i, _vp]),

@@ -1,0 +1,149 @@
+// Byte movers for the layout operations on either side of the matmul: a strided view made
+// contiguous (Tensor::contiguous / clone, i.e. TensorImpl::clone_as_contiguous), ops::Slice,
+// ops::Concat and the 2-D ops::Transpose.  All are HBM-bound: every element is read once and
+// written once, so the roofline is 2 * bytes / HBM bandwidth.
+//
+//   strided_copy_kernel   an n-dimensional box whose innermost run is contiguous on both sides:
+//                         one thread per vector of up to 16 bytes, coordinates decoded with
+//                         multiply-shift division, loads and stores coalesced along the run.
+//                         Also the element-by-element fallback (vector = one element) for
+//                         views with no contiguous run at all.
+//   tiled_transpose_kernel views whose innermost index is NOT the contiguous one but another
+//                         index is (a transposed or permuted view): tiles of the plane spanned
+//                         by the two indices go through shared memory, so reads are coalesced
+//                         along the source's contiguous index and writes along the
+//                         destination's.
+//
+// The reference does the first job with one thread per element and a per-byte copy loop after
+// allocating and copying its shape metadata per call (src/backend/cuda/repack.cu:5-54), the
+// slices and concatenations with per-element coordinate kernels on managed-memory metadata
+// (src/backend/cuda/slice.cu:7-114, concat.cu:8-158) and the 2-D transpose with a per-element
+// kernel (src/backend/cuda/transpose.cu:8-51).
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace tvb {
+
+constexpr int kMaxLayoutDims = 8;
+
+// n / d for n < 2^31 by multiply-high and shift (d >= 1).
+struct FastDiv {
+  uint32_t d, m, s;
+};
+inline FastDiv make_fastdiv(uint32_t d) {
+  FastDiv f;
+  f.d = d;
+  uint32_t s = 0;
+  while ((1ull << s) < d) ++s;
+  f.s = s;
+  f.m = static_cast<uint32_t>(((1ull << 32) * ((1ull << s) - d)) / d + 1);
+  return f;
+}
+__device__ __forceinline__ uint32_t fast_div(uint32_t n, const FastDiv& f) {
+  return (__umulhi(n, f.m) + n) >> f.s;
+}
+
+// A box of `ndim` indices (index 0 outermost).  The innermost index counts VECTORS of the
+// kernel's copy type; strides are in bytes on both sides.
+struct BoxParams {
+  int32_t ndim;
+  uint32_t size[kMaxLayoutDims];
+  FastDiv div[kMaxLayoutDims];
+  int64_t src_stride[kMaxLayoutDims];
+  int64_t dst_stride[kMaxLayoutDims];
+};
+
+// V = copy type (uint8_t, uint16_t, uint32_t, uint64_t or uint4).  total < 2^31.
+template <typename V>
+__global__ void __launch_bounds__(256)
+strided_copy_kernel(const char* __restrict__ src, char* __restrict__ dst, uint32_t total, const BoxParams p) {
+  const uint32_t stride = gridDim.x * blockDim.x;
+  for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+    uint32_t rem = idx;
+    int64_t so = 0, dof = 0;
+#pragma unroll
+    for (int i = kMaxLayoutDims - 1; i >= 1; --i) {
+      if (i < p.ndim) {
+        const uint32_t q = fast_div(rem, p.div[i]);
+        const uint32_t c = rem - q * p.size[i];
+        so += static_cast<int64_t>(c) * p.src_stride[i];
+        dof += static_cast<int64_t>(c) * p.dst_stride[i];
+        rem = q;
+      }
+    }
+    so += static_cast<int64_t>(rem) * p.src_stride[0];
+    dof += static_cast<int64_t>(rem) * p.dst_stride[0];
+    *reinterpret_cast<V*>(dst + dof) = *reinterpret_cast<const V*>(src + so);
+  }
+}
+
+// The same for boxes of 2^31 vectors and more: plain 64-bit arithmetic.
+template <typename V>
+__global__ void __launch_bounds__(256)
+strided_copy_kernel_big(const char* __restrict__ src, char* __restrict__ dst, uint64_t total, const BoxParams p) {
+  const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+  for (uint64_t idx = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+    uint64_t rem = idx;
+    int64_t so = 0, dof = 0;
+    for (int i = p.ndim - 1; i >= 1; --i) {
+      const uint64_t q = rem / p.size[i];
+      const uint64_t c = rem - q * p.size[i];
+      so += static_cast<int64_t>(c) * p.src_stride[i];
+      dof += static_cast<int64_t>(c) * p.dst_stride[i];
+      rem = q;
+    }
+    so += static_cast<int64_t>(rem) * p.src_stride[0];
+    dof += static_cast<int64_t>(rem) * p.dst_stride[0];
+    *reinterpret_cast<V*>(dst + dof) = *reinterpret_cast<const V*>(src + so);
+  }
+}
+
+// Transposing copy.  The view has its innermost index `l` (extent nl, source stride sl elements,
+// destination stride 1) and another index `u` (extent nu, source stride 1, destination stride du
+// elements).  The remaining indices form the `outer` box, decoded once per block from
+// blockIdx.z (+ z0); their strides are in elements.  TILE x TILE elements per block, 256 threads.
+struct TransposeParams {
+  int32_t nl, nu;
+  int64_t sl, du;
+  int32_t n_outer;                       // number of outer indices
+  uint32_t osize[kMaxLayoutDims];
+  int64_t osrc[kMaxLayoutDims], odst[kMaxLayoutDims];
+  uint32_t z0;
+};
+
+template <typename T, int TILE>
+__global__ void __launch_bounds__(256)
+tiled_transpose_kernel(const T* __restrict__ src, T* __restrict__ dst, const TransposeParams p) {
+  // +1 word of padding per row keeps both phases free of bank conflicts for 4-byte elements
+  // and at most 2-way for narrower ones
+  __shared__ T tile[TILE][TILE + (sizeof(T) >= 4 ? 1 : 4 / sizeof(T))];
+  uint32_t z = blockIdx.z + p.z0;
+  int64_t so = 0, dof = 0;
+  for (int i = p.n_outer - 1; i >= 0; --i) {
+    const uint32_t q = z / p.osize[i];
+    const uint32_t c = z - q * p.osize[i];
+    so += static_cast<int64_t>(c) * p.osrc[i];
+    dof += static_cast<int64_t>(c) * p.odst[i];
+    z = q;
+  }
+  const int u0 = blockIdx.x * TILE, l0 = blockIdx.y * TILE;
+  constexpr int ROWS_PER_PASS = 256 / TILE;   // TILE = 32: 8 rows per pass, TILE = 64: 4
+  const int tx = threadIdx.x % TILE, ty = threadIdx.x / TILE;
+  // read: rows of the tile run along u (contiguous in the source)
+#pragma unroll
+  for (int r = ty; r < TILE; r += ROWS_PER_PASS) {
+    const int l = l0 + r, u = u0 + tx;
+    if (l < p.nl && u < p.nu) tile[r][tx] = src[so + static_cast<int64_t>(l) * p.sl + u];
+  }
+  __syncthreads();
+  // write: rows run along l (contiguous in the destination)
+#pragma unroll
+  for (int r = ty; r < TILE; r += ROWS_PER_PASS) {
+    const int u = u0 + r, l = l0 + tx;
+    if (u < p.nu && l < p.nl) dst[dof + static_cast<int64_t>(u) * p.du + l] = tile[tx][r];
+  }
+}
+
+}  // namespace tvb

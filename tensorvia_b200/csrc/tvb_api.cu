@@ -16,6 +16,8 @@
 
 #include "aux_kernels.cuh"
 #include "block_pool.h"
+#include "layout_kernels.cuh"
+#include "layout_plan.h"
 #include "simt_gemm.cuh"
 #include "tvb.h"
 #include "umma_gemm.cuh"
@@ -802,6 +804,127 @@ cudaError_t launch_fill(void* dst, size_t n, uint64_t seed, uint64_t first, int 
   return cudaGetLastError();
 }
 
+// ------------------------------------------------------------------------------------
+// layout operations: one strided box copy behind repack, slice, concat and transpose
+// ------------------------------------------------------------------------------------
+template <typename V>
+cudaError_t launch_strided_copy(Context* c, const void* src, void* dst, const CopyPlan& plan, size_t es,
+                                cudaStream_t s) {
+  BoxParams bp{};
+  bp.ndim = plan.ndim;
+  uint64_t total = 1;
+  for (int i = 0; i < plan.ndim; ++i) {
+    const bool last = i == plan.ndim - 1;
+    // the innermost index counts vectors of V when it is the contiguous run
+    const uint64_t size = (last && plan.kind == CopyKind::kVector)
+                              ? static_cast<uint64_t>(plan.dim[i].size) * es / sizeof(V)
+                              : static_cast<uint64_t>(plan.dim[i].size);
+    const int64_t unit = (last && plan.kind == CopyKind::kVector) ? static_cast<int64_t>(sizeof(V))
+                                                                  : static_cast<int64_t>(es);
+    if (size > 0xFFFFFFFFull) return cudaErrorInvalidValue;
+    bp.size[i] = static_cast<uint32_t>(size);
+    bp.div[i] = make_fastdiv(static_cast<uint32_t>(size));
+    bp.src_stride[i] = plan.dim[i].sstride * unit;
+    bp.dst_stride[i] = plan.dim[i].dstride * unit;
+    total *= size;
+  }
+  uint64_t blocks = (total + 255) / 256;
+  const uint64_t cap = static_cast<uint64_t>(c->sm_count) * 32;
+  if (blocks > cap) blocks = cap;
+  if (blocks == 0) blocks = 1;
+  if (total < 0x80000000ull)
+    strided_copy_kernel<V><<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+        static_cast<const char*>(src), static_cast<char*>(dst), static_cast<uint32_t>(total), bp);
+  else
+    strided_copy_kernel_big<V><<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+        static_cast<const char*>(src), static_cast<char*>(dst), total, bp);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError();
+}
+
+template <typename T, int TILE>
+cudaError_t launch_tiled_transpose(const void* src, void* dst, const CopyPlan& plan, cudaStream_t s) {
+  TransposeParams tp{};
+  const LayoutDim& l = plan.dim[plan.ndim - 1];
+  const LayoutDim& u = plan.dim[plan.unit_dim];
+  tp.nl = static_cast<int32_t>(l.size);
+  tp.nu = static_cast<int32_t>(u.size);
+  tp.sl = l.sstride;
+  tp.du = u.dstride;
+  uint64_t outer = 1;
+  for (int i = 0; i < plan.ndim - 1; ++i) {
+    if (i == plan.unit_dim) continue;
+    if (plan.dim[i].size > 0xFFFFFFFFll) return cudaErrorInvalidValue;
+    tp.osize[tp.n_outer] = static_cast<uint32_t>(plan.dim[i].size);
+    tp.osrc[tp.n_outer] = plan.dim[i].sstride;
+    tp.odst[tp.n_outer] = plan.dim[i].dstride;
+    ++tp.n_outer;
+    outer *= static_cast<uint64_t>(plan.dim[i].size);
+  }
+  if (outer > 0xFFFFFFFFull) return cudaErrorInvalidValue;
+  const unsigned gx = static_cast<unsigned>((tp.nu + TILE - 1) / TILE), gy = static_cast<unsigned>((tp.nl + TILE - 1) / TILE);
+  for (uint64_t z0 = 0; z0 < outer; z0 += 65535) {
+    const unsigned gz = static_cast<unsigned>(outer - z0 < 65535 ? outer - z0 : 65535);
+    tp.z0 = static_cast<uint32_t>(z0);
+    tiled_transpose_kernel<T, TILE><<<dim3(gx, gy, gz), 256, 0, s>>>(static_cast<const T*>(src), static_cast<T*>(dst), tp);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+  }
+  return cudaSuccess;
+}
+
+// dst box <- src box, strides in elements of `es` bytes
+int copy_box(Context* c, const void* src, void* dst, size_t es, const LayoutDim* dims, int n, cudaStream_t s) {
+  for (int i = 0; i < n; ++i) {
+    if (dims[i].size <= 0) return fail(TVB_ERR_SHAPE, "extent %d is %lld: extents must be positive", i, (long long)dims[i].size);
+    if (dims[i].sstride < 0 || dims[i].dstride < 0) return fail(TVB_ERR_INVALID_ARG, "negative strides are not supported");
+  }
+  const CopyPlan plan = plan_copy(dims, n, es, reinterpret_cast<uintptr_t>(src), reinterpret_cast<uintptr_t>(dst));
+  cudaError_t e = cudaSuccess;
+  switch (plan.kind) {
+    case CopyKind::kContiguous:
+      e = cudaMemcpyAsync(dst, src, static_cast<size_t>(plan.dim[0].size) * es, cudaMemcpyDeviceToDevice, s);
+      break;
+    case CopyKind::kVector:
+      switch (plan.vector_bytes) {
+        case 16: e = launch_strided_copy<uint4>(c, src, dst, plan, es, s); break;
+        case 8: e = launch_strided_copy<uint64_t>(c, src, dst, plan, es, s); break;
+        case 4: e = launch_strided_copy<uint32_t>(c, src, dst, plan, es, s); break;
+        case 2: e = launch_strided_copy<uint16_t>(c, src, dst, plan, es, s); break;
+        default: e = launch_strided_copy<uint8_t>(c, src, dst, plan, es, s); break;
+      }
+      break;
+    case CopyKind::kTranspose:
+      switch (es) {
+        case 1: e = launch_tiled_transpose<uint8_t, 64>(src, dst, plan, s); break;
+        case 2: e = launch_tiled_transpose<uint16_t, 64>(src, dst, plan, s); break;
+        case 4: e = launch_tiled_transpose<uint32_t, 32>(src, dst, plan, s); break;
+        default: e = launch_tiled_transpose<uint64_t, 32>(src, dst, plan, s); break;
+      }
+      break;
+    case CopyKind::kElement:
+      switch (es) {
+        case 1: e = launch_strided_copy<uint8_t>(c, src, dst, plan, es, s); break;
+        case 2: e = launch_strided_copy<uint16_t>(c, src, dst, plan, es, s); break;
+        case 4: e = launch_strided_copy<uint32_t>(c, src, dst, plan, es, s); break;
+        default: e = launch_strided_copy<uint64_t>(c, src, dst, plan, es, s); break;
+      }
+      break;
+  }
+  if (e != cudaSuccess) return fail(TVB_ERR_CUDA, "layout copy failed: %s", cudaGetErrorString(e));
+  return TVB_OK;
+}
+
+int layout_prologue(int device, const void* src, void* dst, int dtype, int ndim, Context** c) {
+  int rc = get_ctx(device, c);
+  if (rc != TVB_OK) return rc;
+  if (!src || !dst) return fail(TVB_ERR_INVALID_ARG, "src and dst must not be null");
+  if (!valid_dtype(dtype)) return fail(TVB_ERR_DTYPE, "dtype out of range: %d", dtype);
+  if (ndim < 1 || ndim > kMaxLayoutDims) return fail(TVB_ERR_SHAPE, "ndim must be 1..%d, got %d", kMaxLayoutDims, ndim);
+  return TVB_OK;
+}
+
 }  // namespace
 
 namespace tvb {
@@ -1232,6 +1355,95 @@ int tvb_fill_splitmix(int device, void* dst, int dtype, uint64_t count, uint64_t
   }
   if (e != cudaSuccess) return fail(TVB_ERR_CUDA, "fill launch failed: %s", cudaGetErrorString(e));
   return TVB_OK;
+}
+
+int tvb_repack(int device, const void* src, void* dst, int dtype, int ndim, const int64_t* shape,
+               const int64_t* strides, void* stream) {
+  Context* c = nullptr;
+  int rc = layout_prologue(device, src, dst, dtype, ndim, &c);
+  if (rc != TVB_OK) return rc;
+  if (!shape || !strides) return fail(TVB_ERR_INVALID_ARG, "shape and strides must not be null");
+  DeviceGuard guard(device);
+  LayoutDim d[kMaxLayoutDims];
+  int64_t dense = 1;
+  for (int i = ndim - 1; i >= 0; --i) {
+    d[i] = LayoutDim{shape[i], strides[i], dense};
+    if (shape[i] > 0) dense *= shape[i];
+  }
+  return copy_box(c, src, dst, dtype_size(dtype), d, ndim, stream ? static_cast<cudaStream_t>(stream) : c->stream);
+}
+
+int tvb_slice(int device, const void* src, void* dst, int dtype, int ndim, const int64_t* shape, int nranges,
+              const int64_t* begin, const int64_t* end, void* stream) {
+  Context* c = nullptr;
+  int rc = layout_prologue(device, src, dst, dtype, ndim, &c);
+  if (rc != TVB_OK) return rc;
+  if (!shape || (nranges > 0 && (!begin || !end))) return fail(TVB_ERR_INVALID_ARG, "shape, begin and end must not be null");
+  if (nranges < 0 || nranges > ndim) return fail(TVB_ERR_SHAPE, "%d ranges for %d dimensions", nranges, ndim);
+  DeviceGuard guard(device);
+  const size_t es = dtype_size(dtype);
+  LayoutDim d[kMaxLayoutDims];
+  int64_t sstride[kMaxLayoutDims];
+  int64_t acc = 1, offset = 0;
+  for (int i = ndim - 1; i >= 0; --i) {
+    if (shape[i] <= 0) return fail(TVB_ERR_SHAPE, "extent %d is %lld: extents must be positive", i, (long long)shape[i]);
+    sstride[i] = acc;
+    acc *= shape[i];
+  }
+  for (int i = 0; i < ndim; ++i) {
+    const int64_t b = i < nranges ? begin[i] : 0, e = i < nranges ? end[i] : shape[i];
+    // the checks of ops::Slice (src/ops.cpp:166-174), plus: an empty window has no tensor
+    if (b < 0 || b >= e || e > shape[i])
+      return fail(TVB_ERR_SHAPE, "range %d is [%lld, %lld) of %lld", i, (long long)b, (long long)e, (long long)shape[i]);
+    d[i].size = e - b;
+    d[i].sstride = sstride[i];
+    offset += b * sstride[i];
+  }
+  int64_t dense = 1;
+  for (int i = ndim - 1; i >= 0; --i) {
+    d[i].dstride = dense;
+    dense *= d[i].size;
+  }
+  return copy_box(c, static_cast<const char*>(src) + offset * static_cast<int64_t>(es), dst, es, d, ndim,
+                  stream ? static_cast<cudaStream_t>(stream) : c->stream);
+}
+
+int tvb_concat(int device, int count, const void* const* srcs, void* dst, int dtype, int ndim, const int64_t* shape,
+               const int64_t* dim_sizes, int dim, void* stream) {
+  Context* c = nullptr;
+  if (count <= 0 || !srcs) return fail(TVB_ERR_INVALID_ARG, "tensors is empty");
+  int rc = layout_prologue(device, srcs[0], dst, dtype, ndim, &c);
+  if (rc != TVB_OK) return rc;
+  if (!shape || !dim_sizes) return fail(TVB_ERR_INVALID_ARG, "shape and dim_sizes must not be null");
+  if (dim < 0 || dim >= ndim) return fail(TVB_ERR_SHAPE, "dim %d out of range for %d dimensions", dim, ndim);
+  DeviceGuard guard(device);
+  const size_t es = dtype_size(dtype);
+  int64_t outer = 1, inner = 1, total = 0;
+  for (int i = 0; i < ndim; ++i) {
+    if (i != dim && shape[i] <= 0) return fail(TVB_ERR_SHAPE, "extent %d is %lld: extents must be positive", i, (long long)shape[i]);
+    if (i < dim) outer *= shape[i];
+    if (i > dim) inner *= shape[i];
+  }
+  for (int t = 0; t < count; ++t) {
+    if (!srcs[t]) return fail(TVB_ERR_INVALID_ARG, "tensor %d is null", t);
+    if (dim_sizes[t] <= 0) return fail(TVB_ERR_SHAPE, "tensor %d has extent %lld along dim %d", t, (long long)dim_sizes[t], dim);
+    total += dim_sizes[t];
+  }
+  cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : c->stream;
+  int64_t at = 0;
+  for (int t = 0; t < count; ++t) {
+    // part t: `outer` runs of dim_sizes[t] * inner elements, landing total * inner apart
+    const LayoutDim d[2] = {{outer, dim_sizes[t] * inner, total * inner}, {dim_sizes[t] * inner, 1, 1}};
+    rc = copy_box(c, srcs[t], static_cast<char*>(dst) + at * inner * static_cast<int64_t>(es), es, d, 2, s);
+    if (rc != TVB_OK) return rc;
+    at += dim_sizes[t];
+  }
+  return TVB_OK;
+}
+
+int tvb_transpose2d(int device, const void* src, void* dst, int dtype, int64_t rows, int64_t cols, void* stream) {
+  const int64_t shape[2] = {cols, rows}, strides[2] = {1, cols};
+  return tvb_repack(device, src, dst, dtype, 2, shape, strides, stream);
 }
 
 int tvb_shard_range(int64_t units, int64_t granule, int parts, int index, int64_t* begin, int64_t* count) {
