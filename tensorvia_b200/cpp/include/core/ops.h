@@ -1,6 +1,7 @@
 // Operators of the host layer: the matmul of the reference (include/core/ops.h:57-59) and the
 // few creation helpers its callers need.
 #pragma once
+#include <utility>
 #include <vector>
 
 #include "tensor.h"
@@ -13,10 +14,22 @@ namespace ops {
 // unequal common dimension — the checks and messages of the reference's ops::Mul
 // (src/ops.cpp:540-556).  The result dtype is via::compute_type(a.dtype(), b.dtype()).
 // CUDA operands are multiplied on the GPU; host operands are copied in, multiplied on the
-// GPU and the result copied back (there is no CPU kernel in this library).
+// GPU and the result copied back (there is no CPU kernel in this library).  Operands may be
+// views made by t(), permute() or slice(): they are read through their strides, no copy.
 Tensor Mul(const Tensor& a, const Tensor& b);
 // the name the reference's README uses for the same function
 inline Tensor matmul(const Tensor& a, const Tensor& b) { return Mul(a, b); }
+
+// ---- layout operations either side of the matmul (the scatter and gather steps of a sharded
+// product are exactly these) -------------------------------------------------------------------
+// A dense copy of the window [first, second) of every dimension; one range per dimension.
+// Checks and messages of the reference's ops::Slice (src/ops.cpp:158-174).
+Tensor Slice(const Tensor& t, const std::vector<std::pair<int64_t, int64_t>>& ranges);
+// Tensors that agree in dtype, rank and every extent but `dim`, joined along `dim`; checks and
+// messages of the reference's ops::Concat (src/ops.cpp:1301-1316).  One tensor is returned as is.
+Tensor Concat(const std::vector<Tensor>& tensors, int dim);
+// In-place transpose of a 2-D tensor (src/ops.cpp:1334-1353): the storage is rewritten.
+void Transpose(Tensor& a);
 
 Tensor Zeros(const std::vector<int64_t>& shape, via::DataType dtype);
 Tensor Ones(const std::vector<int64_t>& shape, via::DataType dtype);

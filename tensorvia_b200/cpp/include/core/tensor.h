@@ -1,12 +1,14 @@
 // Tensor value type of the host layer: the subset of the reference's include/core/tensor.h
 // that ops::Mul and its callers use.  A Tensor is metadata plus a shared storage object
 // (TensorImpl); copying a Tensor deep-copies the storage, moving is cheap — the reference's
-// value semantics (src/tensor.cpp:396-421).
+// value semantics (src/tensor.cpp:396-421).  t(), permute() and slice() return VIEWS that
+// share the storage (src/tensor.cpp:217-283): only shape, strides and offset change.
 #pragma once
 #include <cstddef>
 #include <cstdint>
 #include <initializer_list>
 #include <memory>
+#include <utility>
 #include <vector>
 
 #include "type_traits.h"
@@ -19,7 +21,7 @@ struct Metadata {
   via::Device device = via::Device::CPU;
   via::DataType dtype = via::DataType::FLOAT32;
   std::vector<int64_t> shape;
-  std::vector<int64_t> strides;  // in elements, dense row-major
+  std::vector<int64_t> strides;  // in elements; dense row-major unless the tensor is a view
   void calculate_strides() {
     strides.assign(shape.size(), 1);
     for (size_t i = shape.size(); i-- > 1;) strides[i - 1] = strides[i] * shape[i];
@@ -71,7 +73,26 @@ class Tensor {
   int64_t shape(int i) const;
   std::vector<int64_t> shape() const { return m_meta.shape; }
   std::vector<int64_t> strides() const { return m_meta.strides; }
-  bool is_contiguous() const { return true; }  // this layer creates no strided views
+  int64_t offset() const { return m_meta.offset; }
+  // strides equal to the dense row-major ones of the shape (src/tensor.cpp:312-322); a window of
+  // leading rows passes although its offset is not zero
+  bool is_contiguous() const;
+  // first element of the view: storage base + offset (data() is the storage base, as in the
+  // reference)
+  const void* view_data() const;
+
+  // Views (no copy).  t(): the two axes of a 2-D tensor swapped; permute(): any order of the
+  // axes, negative indices count from the end; slice(): [first, second) per leading axis,
+  // negative bounds count from the end and bounds are clamped (src/tensor.cpp:217-283).
+  // Unlike the reference, a view of a view composes (its t()/permute() reset the offset to 0).
+  Tensor t();
+  Tensor permute(std::initializer_list<int64_t> dims) const;
+  Tensor permute(const std::vector<int64_t>& dims) const;
+  Tensor slice(const std::vector<std::pair<int64_t, int64_t>>& ranges) const;
+  // a dense copy of what the view shows (src/tensor.cpp:303-310, 324-329); honours the offset
+  // in every case (the reference drops it for a window of leading rows)
+  Tensor contiguous() const;
+  Tensor& to_contiguous();
   std::shared_ptr<TensorImpl> get_impl() const { return m_impl; }
 
   Tensor clone() const;
@@ -96,6 +117,8 @@ class Tensor {
  private:
   friend Tensor tvhost::adopt(std::vector<int64_t>, via::DataType, std::shared_ptr<TensorImpl>, via::Device);
   void read_element(size_t index, void* out) const;
+  Tensor make_view(std::vector<int64_t> shape, std::vector<int64_t> strides, int64_t offset) const;
+  bool is_dense() const { return m_meta.offset == 0 && is_contiguous(); }
   Metadata m_meta;
   std::shared_ptr<TensorImpl> m_impl;
 };
@@ -104,7 +127,7 @@ template <typename T>
 T Tensor::at(std::initializer_list<int64_t> idxs) const {
   if (idxs.size() != m_meta.shape.size()) throw std::runtime_error("at(): wrong number of indices");
   if (sizeof(T) != via::calc_dtype_size(m_meta.dtype)) throw std::runtime_error("at(): element size mismatch");
-  size_t flat = 0, d = 0;
+  size_t flat = static_cast<size_t>(m_meta.offset), d = 0;
   for (int64_t i : idxs) {
     if (i < 0 || i >= m_meta.shape[d]) throw std::runtime_error("at(): index out of range");
     flat += static_cast<size_t>(i) * static_cast<size_t>(m_meta.strides[d++]);

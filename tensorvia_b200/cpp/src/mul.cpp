@@ -24,9 +24,21 @@ Tensor MulImpl<Device::CUDA>::execute(const Tensor& a, const Tensor& b) {
 
   // the result is created on the operands' device, from the pool
   auto sc = std::make_shared<tvhost::CudaStorage>(nullptr, static_cast<size_t>(batch * M * N), res_type, sa->cuda());
-  tvhost::check(tvb_matmul(dev, a.data(), b.data(), sc->data(), static_cast<int>(a.dtype()), static_cast<int>(b.dtype()),
-                           static_cast<int>(res_type), batch, M, K, N, nullptr),
-                "tvb_matmul");
+  // Operands may be views (t(), permute(), slice()): the GEMM reads them through their strides.
+  // (The reference multiplies the underlying buffer as if it were dense, mul.cu:53-56.)
+  auto strides3 = [&](const Tensor& t, int64_t out[3]) {
+    const std::vector<int64_t> st = t.strides();
+    out[0] = batched ? st[0] : 0;
+    out[1] = st[batched ? 1 : 0];
+    out[2] = st[batched ? 2 : 1];
+  };
+  int64_t as[3], bs[3];
+  strides3(a, as);
+  strides3(b, bs);
+  tvhost::check(tvb_matmul_strided(dev, a.view_data(), b.view_data(), sc->data(), static_cast<int>(a.dtype()),
+                                   static_cast<int>(b.dtype()), static_cast<int>(res_type), batch, M, K, N, as, bs,
+                                   nullptr, TVB_ALGO_AUTO),
+                "tvb_matmul_strided");
   sa->cuda()->wait();  // every op of the reference returns with its result complete (mul.cu:122)
 
   std::vector<int64_t> shape = batched ? std::vector<int64_t>{batch, M, N} : std::vector<int64_t>{M, N};

@@ -62,7 +62,26 @@ void HostStorage::copy_to(std::shared_ptr<TensorImpl> dst) const {
 std::unique_ptr<TensorImpl> HostStorage::clone() const {
   return std::make_unique<HostStorage>(m_data, m_numel, m_dtype);
 }
-std::unique_ptr<TensorImpl> HostStorage::clone_as_contiguous(const Metadata&) const { return clone(); }
+// element idx (row-major over the view's shape) comes from storage[offset + sum coord * stride]
+// (the reference's CPU tensor: include/backend/cpu/cpu_tensor.cpp:32-60)
+std::unique_ptr<TensorImpl> HostStorage::clone_as_contiguous(const Metadata& meta) const {
+  auto out = std::make_unique<HostStorage>(nullptr, meta.numel, m_dtype);
+  const size_t es = calc_dtype_size(m_dtype);
+  const char* src = static_cast<const char*>(m_data) + static_cast<size_t>(meta.offset) * es;
+  char* dst = static_cast<char*>(out->data());
+  const size_t nd = meta.shape.size();
+  std::vector<int64_t> coord(nd, 0);
+  for (size_t idx = 0; idx < meta.numel; ++idx) {
+    int64_t off = 0;
+    for (size_t d = 0; d < nd; ++d) off += coord[d] * meta.strides[d];
+    std::memcpy(dst + idx * es, src + off * static_cast<int64_t>(es), es);
+    for (size_t d = nd; d-- > 0;) {
+      if (++coord[d] < meta.shape[d]) break;
+      coord[d] = 0;
+    }
+  }
+  return out;
+}
 std::shared_ptr<ContextImpl> HostStorage::context() const {
   static auto ctx = std::make_shared<HostContext>();
   return ctx;
@@ -95,7 +114,16 @@ std::unique_ptr<TensorImpl> CudaStorage::clone() const {
   m_ctx->wait();
   return c;
 }
-std::unique_ptr<TensorImpl> CudaStorage::clone_as_contiguous(const Metadata&) const { return clone(); }
+// the view gathered on the device (the reference: include/backend/cuda/cuda_tensor.cpp:52-56)
+std::unique_ptr<TensorImpl> CudaStorage::clone_as_contiguous(const Metadata& meta) const {
+  auto out = std::make_unique<CudaStorage>(nullptr, meta.numel, m_dtype, m_ctx);
+  const char* src = static_cast<const char*>(m_data) + static_cast<size_t>(meta.offset) * calc_dtype_size(m_dtype);
+  check(tvb_repack(m_ctx->device(), src, out->data(), static_cast<int>(m_dtype), static_cast<int>(meta.shape.size()),
+                   meta.shape.data(), meta.strides.data(), nullptr),
+        "tvb_repack");
+  m_ctx->wait();
+  return out;
+}
 std::shared_ptr<ContextImpl> CudaStorage::context() const { return m_ctx; }
 
 }  // namespace tvhost

@@ -1,7 +1,9 @@
 // Tensor: construction, value semantics, host/device moves, creation helpers.
+#include <algorithm>
 #include <cstring>
 #include <mutex>
 #include <random>
+#include <string>
 
 #include "factory.h"
 #include "ops.h"
@@ -73,10 +75,15 @@ Tensor::Tensor(void* ptr, std::vector<int64_t> shape, DataType dtype, Device dev
   m_impl = create_tensor_impl(ptr, m_meta.numel, dtype, device);
 }
 
+// A copy owns dense storage: a view is gathered (the reference clones the whole storage and
+// relabels it with dense strides, src/tensor.cpp:396-403, which scrambles a view).
 Tensor::Tensor(const Tensor& other) : m_meta(other.m_meta) {
+  if (other.m_impl) {
+    m_impl = other.is_dense() ? std::shared_ptr<TensorImpl>(other.m_impl->clone())
+                              : std::shared_ptr<TensorImpl>(other.m_impl->clone_as_contiguous(other.m_meta));
+  }
   m_meta.offset = 0;
   m_meta.calculate_strides();
-  m_impl = other.m_impl ? std::shared_ptr<TensorImpl>(other.m_impl->clone()) : nullptr;
 }
 Tensor& Tensor::operator=(const Tensor& other) {
   if (this != &other) {
@@ -98,8 +105,84 @@ int64_t Tensor::shape(int i) const {
 
 Tensor Tensor::clone() const { return Tensor(*this); }
 
+bool Tensor::is_contiguous() const {
+  Metadata dense;
+  dense.shape = m_meta.shape;
+  dense.calculate_strides();
+  return dense.strides == m_meta.strides;
+}
+
+const void* Tensor::view_data() const {
+  if (!m_impl) return nullptr;
+  return static_cast<const char*>(m_impl->data()) + static_cast<size_t>(m_meta.offset) * calc_dtype_size(m_meta.dtype);
+}
+
+Tensor Tensor::make_view(std::vector<int64_t> shape, std::vector<int64_t> strides, int64_t offset) const {
+  Tensor v;
+  v.m_meta.numel = calc_numel(shape);
+  v.m_meta.dtype = m_meta.dtype;
+  v.m_meta.device = m_meta.device;
+  v.m_meta.offset = offset;
+  v.m_meta.shape = std::move(shape);
+  v.m_meta.strides = std::move(strides);
+  v.m_impl = m_impl;
+  return v;
+}
+
+Tensor Tensor::t() {
+  if (m_meta.shape.size() != 2) throw std::runtime_error("t() needs a 2-D tensor");
+  return make_view({m_meta.shape[1], m_meta.shape[0]}, {m_meta.strides[1], m_meta.strides[0]}, m_meta.offset);
+}
+
+Tensor Tensor::permute(std::initializer_list<int64_t> dims) const { return permute(std::vector<int64_t>(dims)); }
+
+Tensor Tensor::permute(const std::vector<int64_t>& dims) const {
+  const int64_t n = static_cast<int64_t>(m_meta.shape.size());
+  if (static_cast<int64_t>(dims.size()) != n)
+    throw std::invalid_argument("permute: number of dims (" + std::to_string(dims.size()) +
+                                ") doesn't match tensor dim (" + std::to_string(n) + ")");
+  std::vector<bool> seen(dims.size(), false);
+  std::vector<int64_t> shape, strides;
+  for (int64_t d : dims) {
+    const int64_t k = d >= 0 ? d : d + n;
+    if (k < 0 || k >= n) throw std::invalid_argument("Dimension out of range");
+    if (seen[static_cast<size_t>(k)]) throw std::invalid_argument("Duplicate dimension in permute");
+    seen[static_cast<size_t>(k)] = true;
+    shape.push_back(m_meta.shape[static_cast<size_t>(k)]);
+    strides.push_back(m_meta.strides[static_cast<size_t>(k)]);
+  }
+  return make_view(std::move(shape), std::move(strides), m_meta.offset);
+}
+
+Tensor Tensor::slice(const std::vector<std::pair<int64_t, int64_t>>& ranges) const {
+  if (ranges.size() > m_meta.shape.size()) throw std::invalid_argument("Too many slice ranges");
+  std::vector<int64_t> shape = m_meta.shape;
+  int64_t offset = m_meta.offset;
+  for (size_t i = 0; i < ranges.size(); ++i) {
+    const int64_t n = m_meta.shape[i];
+    int64_t lo = ranges[i].first < 0 ? ranges[i].first + n : ranges[i].first;
+    int64_t hi = ranges[i].second < 0 ? ranges[i].second + n : ranges[i].second;
+    lo = std::min(std::max<int64_t>(lo, 0), n);
+    hi = std::min(std::max(hi, lo), n);
+    shape[i] = hi - lo;
+    offset += lo * m_meta.strides[i];
+  }
+  return make_view(std::move(shape), m_meta.strides, offset);   // calc_numel rejects an empty window
+}
+
+Tensor Tensor::contiguous() const { return Tensor(*this); }
+
+Tensor& Tensor::to_contiguous() {
+  if (is_dense()) return *this;
+  m_impl = std::shared_ptr<TensorImpl>(m_impl->clone_as_contiguous(m_meta));
+  m_meta.offset = 0;
+  m_meta.calculate_strides();
+  return *this;
+}
+
 void Tensor::to_host() {
   if (m_meta.device == Device::CPU) return;
+  to_contiguous();
   auto host = create_tensor_impl(m_meta.numel, m_meta.dtype, Device::CPU);
   copy_device_to_host(m_impl, host, m_meta.dtype);
   m_impl = host;
@@ -108,6 +191,7 @@ void Tensor::to_host() {
 
 void Tensor::to_device(uint32_t id) {
   if (m_meta.device != Device::CPU) return;
+  to_contiguous();
   auto dev = std::make_shared<tvhost::CudaStorage>(nullptr, m_meta.numel, m_meta.dtype,
                                                    tvhost::cuda_context(static_cast<int>(id)));
   copy_host_to_device(m_impl, dev, m_meta.dtype);

@@ -122,6 +122,95 @@ int main() {
       }
     EXPECT(same && in_range);
   }
+  // ---- views: t(), permute(), slice() share the storage and are consumed by ops::Mul as they lie ----
+  {
+    const int M = 70, K = 48, N = 136;
+    std::vector<float> hat(K * M), hbt(N * K);           // stored transposed: [K,M] and [N,K]
+    for (int i = 0; i < K * M; ++i) hat[i] = std::sin(0.21f * i);
+    for (int i = 0; i < N * K; ++i) hbt[i] = std::cos(0.13f * i);
+    Tensor At(hat.data(), {K, M}, DataType::FLOAT32, Device::CUDA), Bt(hbt.data(), {N, K}, DataType::FLOAT32, Device::CUDA);
+    Tensor Av = At.t(), Bv = Bt.t();
+    EXPECT(Av.data() == At.data() && !Av.is_contiguous() && Av.shape() == (std::vector<int64_t>{M, K}));
+    EXPECT(Av.at<float>({3, 5}) == At.at<float>({5, 3}));
+    Tensor C = ops::Mul(Av, Bv);                          // no copy of either operand
+    Tensor C2 = ops::Mul(Av.contiguous(), Bv.contiguous());
+    C.to_host();
+    C2.to_host();
+    const float* c = static_cast<const float*>(C.data());
+    const float* c2 = static_cast<const float*>(C2.data());
+    double num = 0, den = 0, num2 = 0;
+    for (int i = 0; i < M; ++i)
+      for (int j = 0; j < N; ++j) {
+        double s = 0;
+        for (int k = 0; k < K; ++k) s += static_cast<double>(hat[k * M + i]) * hbt[j * K + k];
+        num += (c[i * N + j] - s) * (c[i * N + j] - s);
+        num2 += (c2[i * N + j] - s) * (c2[i * N + j] - s);
+        den += s * s;
+      }
+    EXPECT(std::sqrt(num / den) <= 1e-5 && std::sqrt(num2 / den) <= 1e-5);
+  }
+  {
+    // batched bf16: B given as [b, N, K] and viewed as [b, K, N]; a window of A's rows
+    const int Bt = 2, M = 40, K = 64, N = 24;
+    std::vector<int8_t> ha(Bt * (M + 8) * K), hb(Bt * N * K);
+    for (size_t i = 0; i < ha.size(); ++i) ha[i] = static_cast<int8_t>((i * 29) % 21 - 10);
+    for (size_t i = 0; i < hb.size(); ++i) hb[i] = static_cast<int8_t>((i * 53) % 21 - 10);
+    Tensor Abig(ha.data(), {Bt, M + 8, K}, DataType::INT8, Device::CUDA), Bs(hb.data(), {Bt, N, K}, DataType::INT8, Device::CUDA);
+    Tensor Aw = Abig.slice({{0, Bt}, {4, 4 + M}});
+    Tensor Bv = Bs.permute({0, 2, 1});
+    EXPECT(Aw.offset() == 4 * K && Aw.shape() == (std::vector<int64_t>{Bt, M, K}));
+    Tensor C = ops::Mul(Aw, Bv);
+    int bad = 0;
+    for (int b = 0; b < Bt; ++b)
+      for (int i = 0; i < M; ++i)
+        for (int j = 0; j < N; ++j) {
+          int sacc = 0;
+          for (int k = 0; k < K; ++k) sacc += int(ha[(b * (M + 8) + 4 + i) * K + k]) * int(hb[(b * N + j) * K + k]);
+          if (C.at<int8_t>({b, i, j}) != static_cast<int8_t>(sacc)) ++bad;
+        }
+    EXPECT(bad == 0);
+  }
+  // ---- Slice / Concat / Transpose: the scatter and gather steps of a row-sharded product --------
+  {
+    const int M = 96, K = 32, N = 40;
+    std::vector<float> ha(M * K), hb(K * N);
+    for (int i = 0; i < M * K; ++i) ha[i] = 0.01f * (i % 97) - 0.4f;
+    for (int i = 0; i < K * N; ++i) hb[i] = 0.02f * (i % 53) - 0.5f;
+    Tensor A(ha.data(), {M, K}, DataType::FLOAT32, Device::CUDA), B(hb.data(), {K, N}, DataType::FLOAT32, Device::CUDA);
+    Tensor full = ops::Mul(A, B);
+    std::vector<Tensor> parts;
+    for (int r = 0; r < 3; ++r) parts.push_back(ops::Mul(ops::Slice(A, {{r * 32, r * 32 + 32}, {0, K}}), B));
+    Tensor joined = ops::Concat(parts, 0);
+    EXPECT(joined.shape() == full.shape());
+    bool same = true;
+    for (int i = 0; i < M; i += 7)
+      for (int j = 0; j < N; j += 3) same = same && joined.at<float>({i, j}) == full.at<float>({i, j});
+    EXPECT(same);
+    Tensor T = A.clone();
+    ops::Transpose(T);
+    EXPECT(T.shape() == (std::vector<int64_t>{K, M}) && T.is_contiguous() && T.at<float>({5, 77}) == A.at<float>({77, 5}));
+    Tensor inner = ops::Slice(A, {{10, 20}, {3, 9}});
+    EXPECT(inner.shape() == (std::vector<int64_t>{10, 6}) && inner.at<float>({2, 4}) == A.at<float>({12, 7}));
+    Tensor wide = ops::Concat({inner, inner}, 1);
+    EXPECT(wide.shape() == (std::vector<int64_t>{10, 12}) && wide.at<float>({9, 11}) == A.at<float>({19, 8}));
+    EXPECT(thrown([&] { ops::Slice(A, {}); }) == "Slice ranges cannot be empty");
+    EXPECT(thrown([&] { ops::Slice(A, {{0, 4}}); }) == "Slice ranges size must be equal to tensor shape size");
+    EXPECT(thrown([&] { ops::Slice(A, {{5, 4}, {0, 1}}); }) == "first must be less than second");
+    EXPECT(thrown([&] { ops::Slice(A, {{0, 4}, {0, K + 1}}); }) == "second must be less than 32");
+    EXPECT(thrown([&] { ops::Transpose(full = Tensor::Ones({2, 2, 2})); }) == "transpose only support 2D tensor");
+    bool threw = false;
+    try { ops::Concat({A, Tensor::Ones({M, K}, DataType::INT8)}, 0); } catch (const std::invalid_argument& e) {
+      threw = std::string(e.what()) == "tensors must have same dtype";
+    }
+    EXPECT(threw);
+    // a copy of a view is dense and owns its storage
+    Tensor At = A.t();
+    Tensor copy = At;
+    EXPECT(copy.is_contiguous() && copy.data() != A.data() && copy.at<float>({7, 50}) == A.at<float>({50, 7}));
+    // a window of leading rows: the offset is honoured (the reference returns rows from 0)
+    Tensor rows = A.slice({{8, 12}}).contiguous();
+    EXPECT(rows.at<float>({0, 0}) == A.at<float>({8, 0}) && rows.at<float>({3, 31}) == A.at<float>({11, 31}));
+  }
   std::printf(g_failed ? "%d check(s) failed\n" : "api_check: all checks passed\n", g_failed);
   return g_failed ? 1 : 0;
 }

@@ -12,7 +12,9 @@
 //                         index is (a transposed or permuted view): tiles of the plane spanned
 //                         by the two indices go through shared memory, so reads are coalesced
 //                         along the source's contiguous index and writes along the
-//                         destination's.
+//                         destination's.  tiled_transpose_words_kernel is its form for 1-, 2-
+//                         and 4-byte elements in word-aligned runs: 32-bit global accesses,
+//                         narrow elements transposed in registers.
 //
 // The reference does the first job with one thread per element and a per-byte copy loop after
 // allocating and copying its shape metadata per call (src/backend/cuda/repack.cu:5-54), the
@@ -143,6 +145,78 @@ tiled_transpose_kernel(const T* __restrict__ src, T* __restrict__ dst, const Tra
   for (int r = ty; r < TILE; r += ROWS_PER_PASS) {
     const int u = u0 + r, l = l0 + tx;
     if (u < p.nu && l < p.nl) dst[dof + static_cast<int64_t>(u) * p.du + l] = tile[tx][r];
+  }
+}
+
+// The transposing copy for 1-, 2- and 4-byte elements when every run starts on a 4-byte boundary
+// and holds whole 32-bit words on both sides (extents, strides and bases multiples of SUB
+// elements): global memory is touched only in 32-bit words, 128 bytes per warp and row on the
+// way in, and the SUB x SUB blocks of narrow elements are transposed in registers with byte
+// permutes on the way out.  SUB = elements per word.  A tile holds ROWS values of l by 32 words
+// of u; its shared-memory rows are 33 words long, and the lane-to-item maps below keep every
+// shared-memory access free of bank conflicts.
+template <int SUB>
+__global__ void __launch_bounds__(256)
+tiled_transpose_words_kernel(const char* __restrict__ src, char* __restrict__ dst, const TransposeParams p) {
+  constexpr int ES = 4 / SUB;
+  constexpr int ROWS = SUB == 4 ? 128 : 64;
+  __shared__ uint32_t tile[ROWS][33];
+  uint32_t z = blockIdx.z + p.z0;
+  int64_t so = 0, dof = 0;
+  for (int i = p.n_outer - 1; i >= 0; --i) {
+    const uint32_t q = z / p.osize[i];
+    const uint32_t c = z - q * p.osize[i];
+    so += static_cast<int64_t>(c) * p.osrc[i];
+    dof += static_cast<int64_t>(c) * p.odst[i];
+    z = q;
+  }
+  const char* sbase = src + so * ES;
+  char* dbase = dst + dof * ES;
+  const int u0 = blockIdx.x * 32 * SUB, l0 = blockIdx.y * ROWS;
+#pragma unroll
+  for (int it = threadIdx.x; it < ROWS * 32; it += 256) {
+    const int r = it >> 5, c = it & 31;
+    const int l = l0 + r, u = u0 + c * SUB;
+    if (l < p.nl && u < p.nu)
+      tile[r][c] = *reinterpret_cast<const uint32_t*>(sbase + (static_cast<int64_t>(l) * p.sl + u) * ES);
+  }
+  __syncthreads();
+  auto put = [&](int u, int l, uint32_t w) {
+    if (u < p.nu) *reinterpret_cast<uint32_t*>(dbase + (static_cast<int64_t>(u) * p.du + l) * ES) = w;
+  };
+  if constexpr (SUB == 1) {
+#pragma unroll
+    for (int it = threadIdx.x; it < 64 * 32; it += 256) {
+      const int l = (it & 31) | (((it >> 5) & 1) << 5), uu = it >> 6;
+      if (l0 + l < p.nl) put(u0 + uu, l0 + l, tile[l][uu]);
+    }
+  } else if constexpr (SUB == 2) {
+#pragma unroll
+    for (int it = threadIdx.x; it < 32 * 32; it += 256) {
+      const int lp = (it & 15) | (((it >> 5) & 1) << 4), uw = ((it >> 4) & 1) | ((it >> 6) << 1);
+      const uint32_t w0 = tile[2 * lp][uw], w1 = tile[2 * lp + 1][uw];
+      const int l = l0 + 2 * lp, u = u0 + 2 * uw;
+      if (l < p.nl) {
+        put(u, l, __byte_perm(w0, w1, 0x5410));
+        put(u + 1, l, __byte_perm(w0, w1, 0x7632));
+      }
+    }
+  } else {
+#pragma unroll
+    for (int it = threadIdx.x; it < 32 * 32; it += 256) {
+      const int lq = (it & 7) | (((it >> 5) & 3) << 3), uw = ((it >> 3) & 3) | ((it >> 7) << 2);
+      const uint32_t w0 = tile[4 * lq][uw], w1 = tile[4 * lq + 1][uw], w2 = tile[4 * lq + 2][uw],
+                     w3 = tile[4 * lq + 3][uw];
+      const int l = l0 + 4 * lq, u = u0 + 4 * uw;
+      if (l < p.nl) {
+        const uint32_t t0 = __byte_perm(w0, w1, 0x5140), t1 = __byte_perm(w2, w3, 0x5140);
+        const uint32_t t2 = __byte_perm(w0, w1, 0x7362), t3 = __byte_perm(w2, w3, 0x7362);
+        put(u, l, __byte_perm(t0, t1, 0x5410));
+        put(u + 1, l, __byte_perm(t0, t1, 0x7632));
+        put(u + 2, l, __byte_perm(t2, t3, 0x5410));
+        put(u + 3, l, __byte_perm(t2, t3, 0x7632));
+      }
+    }
   }
 }
 

@@ -842,7 +842,8 @@ cudaError_t launch_strided_copy(Context* c, const void* src, void* dst, const Co
   return cudaGetLastError();
 }
 
-template <typename T, int TILE>
+// SUB = elements per 32-bit word; 0 = the element kernel of type T with TILE x TILE tiles
+template <typename T, int TILE, int SUB>
 cudaError_t launch_tiled_transpose(const void* src, void* dst, const CopyPlan& plan, cudaStream_t s) {
   TransposeParams tp{};
   const LayoutDim& l = plan.dim[plan.ndim - 1];
@@ -862,11 +863,15 @@ cudaError_t launch_tiled_transpose(const void* src, void* dst, const CopyPlan& p
     outer *= static_cast<uint64_t>(plan.dim[i].size);
   }
   if (outer > 0xFFFFFFFFull) return cudaErrorInvalidValue;
-  const unsigned gx = static_cast<unsigned>((tp.nu + TILE - 1) / TILE), gy = static_cast<unsigned>((tp.nl + TILE - 1) / TILE);
+  constexpr int TILE_U = SUB ? 32 * SUB : TILE, TILE_L = SUB ? (SUB == 4 ? 128 : 64) : TILE;
+  const unsigned gx = static_cast<unsigned>((tp.nu + TILE_U - 1) / TILE_U), gy = static_cast<unsigned>((tp.nl + TILE_L - 1) / TILE_L);
   for (uint64_t z0 = 0; z0 < outer; z0 += 65535) {
     const unsigned gz = static_cast<unsigned>(outer - z0 < 65535 ? outer - z0 : 65535);
     tp.z0 = static_cast<uint32_t>(z0);
-    tiled_transpose_kernel<T, TILE><<<dim3(gx, gy, gz), 256, 0, s>>>(static_cast<const T*>(src), static_cast<T*>(dst), tp);
+    if constexpr (SUB != 0)
+      tiled_transpose_words_kernel<SUB><<<dim3(gx, gy, gz), 256, 0, s>>>(static_cast<const char*>(src), static_cast<char*>(dst), tp);
+    else
+      tiled_transpose_kernel<T, TILE><<<dim3(gx, gy, gz), 256, 0, s>>>(static_cast<const T*>(src), static_cast<T*>(dst), tp);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
@@ -895,14 +900,27 @@ int copy_box(Context* c, const void* src, void* dst, size_t es, const LayoutDim*
         default: e = launch_strided_copy<uint8_t>(c, src, dst, plan, es, s); break;
       }
       break;
-    case CopyKind::kTranspose:
+    case CopyKind::kTranspose: {
+      // whole, aligned 32-bit words on both sides: the word kernel
+      bool words = es <= 4 && reinterpret_cast<uintptr_t>(src) % 4 == 0 && reinterpret_cast<uintptr_t>(dst) % 4 == 0;
+      const int64_t sub = static_cast<int64_t>(4 / (es <= 4 ? es : 4));
+      for (int i = 0; words && i < plan.ndim; ++i) {
+        const bool plane = i == plan.ndim - 1 || i == plan.unit_dim;
+        if (plane && plan.dim[i].size % sub != 0) words = false;
+        if (i != plan.unit_dim && plan.dim[i].sstride % sub != 0) words = false;
+        if (i != plan.ndim - 1 && plan.dim[i].dstride % sub != 0) words = false;
+      }
       switch (es) {
-        case 1: e = launch_tiled_transpose<uint8_t, 64>(src, dst, plan, s); break;
-        case 2: e = launch_tiled_transpose<uint16_t, 64>(src, dst, plan, s); break;
-        case 4: e = launch_tiled_transpose<uint32_t, 32>(src, dst, plan, s); break;
-        default: e = launch_tiled_transpose<uint64_t, 32>(src, dst, plan, s); break;
+        case 1: e = words ? launch_tiled_transpose<uint8_t, 64, 4>(src, dst, plan, s)
+                          : launch_tiled_transpose<uint8_t, 64, 0>(src, dst, plan, s); break;
+        case 2: e = words ? launch_tiled_transpose<uint16_t, 64, 2>(src, dst, plan, s)
+                          : launch_tiled_transpose<uint16_t, 64, 0>(src, dst, plan, s); break;
+        case 4: e = words ? launch_tiled_transpose<uint32_t, 32, 1>(src, dst, plan, s)
+                          : launch_tiled_transpose<uint32_t, 32, 0>(src, dst, plan, s); break;
+        default: e = launch_tiled_transpose<uint64_t, 32, 0>(src, dst, plan, s); break;
       }
       break;
+    }
     case CopyKind::kElement:
       switch (es) {
         case 1: e = launch_strided_copy<uint8_t>(c, src, dst, plan, es, s); break;
