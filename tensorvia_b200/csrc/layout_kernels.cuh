@@ -152,15 +152,14 @@ tiled_transpose_kernel(const T* __restrict__ src, T* __restrict__ dst, const Tra
 // and holds whole 32-bit words on both sides (extents, strides and bases multiples of SUB
 // elements): global memory is touched only in 32-bit words, 128 bytes per warp and row on the
 // way in, and the SUB x SUB blocks of narrow elements are transposed in registers with byte
-// permutes on the way out.  SUB = elements per word.  A tile holds ROWS values of l by 32 words
-// of u; its shared-memory rows are 33 words long, and the lane-to-item maps below keep every
+// permutes on the way out.  SUB = elements per word.  A tile holds ROWS values of l by UW words
+// of u; its shared-memory rows are UW + 1 words long, and the lane-to-item maps below keep every
 // shared-memory access free of bank conflicts.
-template <int SUB>
+template <int SUB, int ROWS, int UW>
 __global__ void __launch_bounds__(256)
 tiled_transpose_words_kernel(const char* __restrict__ src, char* __restrict__ dst, const TransposeParams p) {
   constexpr int ES = 4 / SUB;
-  constexpr int ROWS = SUB == 4 ? 128 : 64;
-  __shared__ uint32_t tile[ROWS][33];
+  __shared__ uint32_t tile[ROWS][UW + 1];
   uint32_t z = blockIdx.z + p.z0;
   int64_t so = 0, dof = 0;
   for (int i = p.n_outer - 1; i >= 0; --i) {
@@ -172,10 +171,10 @@ tiled_transpose_words_kernel(const char* __restrict__ src, char* __restrict__ ds
   }
   const char* sbase = src + so * ES;
   char* dbase = dst + dof * ES;
-  const int u0 = blockIdx.x * 32 * SUB, l0 = blockIdx.y * ROWS;
+  const int u0 = blockIdx.x * UW * SUB, l0 = blockIdx.y * ROWS;
 #pragma unroll
-  for (int it = threadIdx.x; it < ROWS * 32; it += 256) {
-    const int r = it >> 5, c = it & 31;
+  for (int it = threadIdx.x; it < ROWS * UW; it += 256) {
+    const int r = it / UW, c = it % UW;
     const int l = l0 + r, u = u0 + c * SUB;
     if (l < p.nl && u < p.nu)
       tile[r][c] = *reinterpret_cast<const uint32_t*>(sbase + (static_cast<int64_t>(l) * p.sl + u) * ES);
@@ -186,14 +185,16 @@ tiled_transpose_words_kernel(const char* __restrict__ src, char* __restrict__ ds
   };
   if constexpr (SUB == 1) {
 #pragma unroll
-    for (int it = threadIdx.x; it < 64 * 32; it += 256) {
-      const int l = (it & 31) | (((it >> 5) & 1) << 5), uu = it >> 6;
+    for (int it = threadIdx.x; it < ROWS * UW; it += 256) {
+      const int l = it % ROWS, uu = it / ROWS;
       if (l0 + l < p.nl) put(u0 + uu, l0 + l, tile[l][uu]);
     }
   } else if constexpr (SUB == 2) {
 #pragma unroll
-    for (int it = threadIdx.x; it < 32 * 32; it += 256) {
-      const int lp = (it & 15) | (((it >> 5) & 1) << 4), uw = ((it >> 4) & 1) | ((it >> 6) << 1);
+    constexpr int LP = ROWS / 2;   // pairs of l per tile
+    for (int it = threadIdx.x; it < LP * UW; it += 256) {
+      // 16 consecutive pairs x 2 words per warp: banks 2*lp + uw are all different
+      const int lp = (it & 15) | (((it >> 5) % (LP / 16)) << 4), uw = ((it >> 4) & 1) | (((it >> 5) / (LP / 16)) << 1);
       const uint32_t w0 = tile[2 * lp][uw], w1 = tile[2 * lp + 1][uw];
       const int l = l0 + 2 * lp, u = u0 + 2 * uw;
       if (l < p.nl) {
@@ -203,8 +204,10 @@ tiled_transpose_words_kernel(const char* __restrict__ src, char* __restrict__ ds
     }
   } else {
 #pragma unroll
-    for (int it = threadIdx.x; it < 32 * 32; it += 256) {
-      const int lq = (it & 7) | (((it >> 5) & 3) << 3), uw = ((it >> 3) & 3) | ((it >> 7) << 2);
+    constexpr int LQ = ROWS / 4;   // quads of l per tile
+    for (int it = threadIdx.x; it < LQ * UW; it += 256) {
+      // 8 consecutive quads x 4 words per warp: banks 4*lq + uw are all different
+      const int lq = (it & 7) | (((it >> 5) % (LQ / 8)) << 3), uw = ((it >> 3) & 3) | (((it >> 5) / (LQ / 8)) << 2);
       const uint32_t w0 = tile[4 * lq][uw], w1 = tile[4 * lq + 1][uw], w2 = tile[4 * lq + 2][uw],
                      w3 = tile[4 * lq + 3][uw];
       const int l = l0 + 4 * lq, u = u0 + 4 * uw;
@@ -217,6 +220,75 @@ tiled_transpose_words_kernel(const char* __restrict__ src, char* __restrict__ ds
         put(u + 3, l, __byte_perm(t2, t3, 0x7632));
       }
     }
+  }
+}
+
+// The transposing copy at full width: 16-byte global accesses on both sides.  Needs every run
+// to start on a 16-byte boundary and to hold whole 16-byte vectors (extents of the two plane
+// indices, all strides and both bases multiples of 16 bytes).  A tile is 128 bytes of u by 128
+// bytes of l.  Each thread loads one 16-byte vector from each of SUB consecutive rows of l,
+// transposes the SUB x SUB blocks of narrow elements in registers, and writes words that hold
+// SUB consecutive values of l into a shared tile whose rows run along l.  That tile is not
+// padded: its 16-byte groups are XOR-swizzled with the source vector index, which makes the
+// word stores of a warp hit 32 different banks and keeps the 16-byte reads of the second
+// phase conflict-free too.
+template <int SUB>
+__global__ void __launch_bounds__(256)
+tiled_transpose_vec_kernel(const char* __restrict__ src, char* __restrict__ dst, const TransposeParams p) {
+  constexpr int ES = 4 / SUB;
+  constexpr int TU = 32 * SUB;   // values of u per tile
+  constexpr int TL = 32 * SUB;   // values of l per tile
+  __shared__ uint4 tile[TU][8];  // [u][32 words along l]
+  uint32_t z = blockIdx.z + p.z0;
+  int64_t so = 0, dof = 0;
+  for (int i = p.n_outer - 1; i >= 0; --i) {
+    const uint32_t q = z / p.osize[i];
+    const uint32_t c = z - q * p.osize[i];
+    so += static_cast<int64_t>(c) * p.osrc[i];
+    dof += static_cast<int64_t>(c) * p.odst[i];
+    z = q;
+  }
+  const char* sbase = src + so * ES;
+  char* dbase = dst + dof * ES;
+  const int u0 = blockIdx.x * TU, l0 = blockIdx.y * TL;
+  {
+    const int uv = threadIdx.x & 7, lg = threadIdx.x >> 3;
+    const int u = u0 + uv * 4 * SUB, l = l0 + lg * SUB;
+    if (u < p.nu && l < p.nl) {
+      uint32_t w[SUB][4];
+#pragma unroll
+      for (int h = 0; h < SUB; ++h) {
+        const uint4 v = *reinterpret_cast<const uint4*>(sbase + (static_cast<int64_t>(l + h) * p.sl + u) * ES);
+        w[h][0] = v.x; w[h][1] = v.y; w[h][2] = v.z; w[h][3] = v.w;
+      }
+      uint32_t* t = reinterpret_cast<uint32_t*>(tile);
+      const int col = lg ^ (uv << 2);
+#pragma unroll
+      for (int m = 0; m < 4; ++m) {
+        const int row = uv * 4 * SUB + m * SUB;
+        if constexpr (SUB == 1) {
+          t[row * 32 + col] = w[0][m];
+        } else if constexpr (SUB == 2) {
+          t[row * 32 + col] = __byte_perm(w[0][m], w[1][m], 0x5410);
+          t[(row + 1) * 32 + col] = __byte_perm(w[0][m], w[1][m], 0x7632);
+        } else {
+          const uint32_t t0 = __byte_perm(w[0][m], w[1][m], 0x5140), t1 = __byte_perm(w[2][m], w[3][m], 0x5140);
+          const uint32_t t2 = __byte_perm(w[0][m], w[1][m], 0x7362), t3 = __byte_perm(w[2][m], w[3][m], 0x7362);
+          t[row * 32 + col] = __byte_perm(t0, t1, 0x5410);
+          t[(row + 1) * 32 + col] = __byte_perm(t0, t1, 0x7632);
+          t[(row + 2) * 32 + col] = __byte_perm(t2, t3, 0x5410);
+          t[(row + 3) * 32 + col] = __byte_perm(t2, t3, 0x7632);
+        }
+      }
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int it = threadIdx.x; it < TU * 8; it += 256) {
+    const int c = it & 7, row = it >> 3;
+    const int u = u0 + row, l = l0 + c * 4 * SUB;
+    if (u < p.nu && l < p.nl)
+      *reinterpret_cast<uint4*>(dbase + (static_cast<int64_t>(u) * p.du + l) * ES) = tile[row][c ^ ((row / (4 * SUB)) & 7)];
   }
 }
 

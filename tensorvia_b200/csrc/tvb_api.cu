@@ -842,8 +842,9 @@ cudaError_t launch_strided_copy(Context* c, const void* src, void* dst, const Co
   return cudaGetLastError();
 }
 
-// SUB = elements per 32-bit word; 0 = the element kernel of type T with TILE x TILE tiles
-template <typename T, int TILE, int SUB>
+// SUB = elements per 32-bit word; 0 = the element kernel of type T with TILE x TILE tiles.
+// VEC: 16-byte accesses (tiled_transpose_vec_kernel) instead of 32-bit ones.
+template <typename T, int TILE, int SUB, bool VEC = false>
 cudaError_t launch_tiled_transpose(const void* src, void* dst, const CopyPlan& plan, cudaStream_t s) {
   TransposeParams tp{};
   const LayoutDim& l = plan.dim[plan.ndim - 1];
@@ -863,13 +864,17 @@ cudaError_t launch_tiled_transpose(const void* src, void* dst, const CopyPlan& p
     outer *= static_cast<uint64_t>(plan.dim[i].size);
   }
   if (outer > 0xFFFFFFFFull) return cudaErrorInvalidValue;
-  constexpr int TILE_U = SUB ? 32 * SUB : TILE, TILE_L = SUB ? (SUB == 4 ? 128 : 64) : TILE;
+  // word tiles: ROWS values of l by UW words of u
+  constexpr int ROWS = SUB == 4 ? 128 : 64, UW = 32;
+  constexpr int TILE_U = VEC ? 32 * SUB : SUB ? UW * SUB : TILE, TILE_L = VEC ? 32 * SUB : SUB ? ROWS : TILE;
   const unsigned gx = static_cast<unsigned>((tp.nu + TILE_U - 1) / TILE_U), gy = static_cast<unsigned>((tp.nl + TILE_L - 1) / TILE_L);
   for (uint64_t z0 = 0; z0 < outer; z0 += 65535) {
     const unsigned gz = static_cast<unsigned>(outer - z0 < 65535 ? outer - z0 : 65535);
     tp.z0 = static_cast<uint32_t>(z0);
-    if constexpr (SUB != 0)
-      tiled_transpose_words_kernel<SUB><<<dim3(gx, gy, gz), 256, 0, s>>>(static_cast<const char*>(src), static_cast<char*>(dst), tp);
+    if constexpr (VEC)
+      tiled_transpose_vec_kernel<SUB><<<dim3(gx, gy, gz), 256, 0, s>>>(static_cast<const char*>(src), static_cast<char*>(dst), tp);
+    else if constexpr (SUB != 0)
+      tiled_transpose_words_kernel<SUB, ROWS, UW><<<dim3(gx, gy, gz), 256, 0, s>>>(static_cast<const char*>(src), static_cast<char*>(dst), tp);
     else
       tiled_transpose_kernel<T, TILE><<<dim3(gx, gy, gz), 256, 0, s>>>(static_cast<const T*>(src), static_cast<T*>(dst), tp);
     g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -910,12 +915,25 @@ int copy_box(Context* c, const void* src, void* dst, size_t es, const LayoutDim*
         if (i != plan.unit_dim && plan.dim[i].sstride % sub != 0) words = false;
         if (i != plan.ndim - 1 && plan.dim[i].dstride % sub != 0) words = false;
       }
+      // whole, aligned 16-byte vectors on both sides: the vector kernel
+      bool vecs = words && reinterpret_cast<uintptr_t>(src) % 16 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0;
+      const int64_t per16 = static_cast<int64_t>(16 / (es <= 4 ? es : 4));
+      for (int i = 0; vecs && i < plan.ndim; ++i) {
+        const bool plane = i == plan.ndim - 1 || i == plan.unit_dim;
+        if (plane && plan.dim[i].size % per16 != 0) vecs = false;
+        if (i != plan.unit_dim && plan.dim[i].sstride % per16 != 0) vecs = false;
+        if (i != plan.ndim - 1 && plan.dim[i].dstride % per16 != 0) vecs = false;
+      }
+      if (getenv("TVB_NO_VEC_TRANSPOSE")) vecs = false;
       switch (es) {
-        case 1: e = words ? launch_tiled_transpose<uint8_t, 64, 4>(src, dst, plan, s)
+        case 1: e = vecs ? launch_tiled_transpose<uint8_t, 64, 4, true>(src, dst, plan, s)
+                  : words ? launch_tiled_transpose<uint8_t, 64, 4>(src, dst, plan, s)
                           : launch_tiled_transpose<uint8_t, 64, 0>(src, dst, plan, s); break;
-        case 2: e = words ? launch_tiled_transpose<uint16_t, 64, 2>(src, dst, plan, s)
+        case 2: e = vecs ? launch_tiled_transpose<uint16_t, 64, 2, true>(src, dst, plan, s)
+                  : words ? launch_tiled_transpose<uint16_t, 64, 2>(src, dst, plan, s)
                           : launch_tiled_transpose<uint16_t, 64, 0>(src, dst, plan, s); break;
-        case 4: e = words ? launch_tiled_transpose<uint32_t, 32, 1>(src, dst, plan, s)
+        case 4: e = vecs ? launch_tiled_transpose<uint32_t, 32, 1, true>(src, dst, plan, s)
+                  : words ? launch_tiled_transpose<uint32_t, 32, 1>(src, dst, plan, s)
                           : launch_tiled_transpose<uint32_t, 32, 0>(src, dst, plan, s); break;
         default: e = launch_tiled_transpose<uint64_t, 32, 0>(src, dst, plan, s); break;
       }

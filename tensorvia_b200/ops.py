@@ -1,4 +1,5 @@
-"""Python face of the matmul operator, for tests, the benchmark and torch users.
+"""Python face of the matmul operator and of the layout operations either side of it, for
+tests, the benchmark and torch users.
 
 It mirrors the reference's `ops::Mul(const Tensor&, const Tensor&)` front end
 (src/ops.cpp:540-573): the same shape rules, the same failures (as RuntimeError,
@@ -114,6 +115,115 @@ def matmul(a, b, *, algo: int = ALGO_AUTO, out=None):
 
 
 Mul = matmul  # the name the reference source uses (include/core/ops.h:59)
+
+# ---- layout operations either side of the matmul ------------------------------------------------
+def _i64(vals):
+    return (C.c_int64 * len(vals))(*[int(v) for v in vals])
+
+
+def _device_call(t):
+    """(device index, stream handle) for a torch CUDA tensor; creates the context on first use."""
+    import torch
+    if t.device.type != "cuda":
+        raise RuntimeError("tensorvia_b200 layout operations need CUDA tensors; there is no CPU path")
+    dev = t.device.index if t.device.index is not None else torch.cuda.current_device()
+    init(dev)
+    return dev, C.c_void_p(torch.cuda.current_stream(t.device).cuda_stream or 1)
+
+
+def contiguous(t):
+    """A dense copy of what a strided view shows: Tensor::contiguous() of the reference
+    (src/tensor.cpp:303-310 -> clone_as_contiguous, src/backend/cuda/repack.cu:5-54), through
+    `tvb_repack`.  The input may be any torch view with non-negative strides."""
+    import torch
+    to_tvb, _ = _torch_maps()
+    if t.dim() == 0 or t.dim() > 8:
+        raise RuntimeError("contiguous: 1 to 8 dimensions")
+    if min(t.stride()) < 0:
+        raise RuntimeError("negative strides are not supported")
+    dev, stream = _device_call(t)
+    out = torch.empty(tuple(t.shape), dtype=t.dtype, device=t.device)
+    check(lib.tvb_repack(dev, t.data_ptr(), out.data_ptr(), to_tvb[t.dtype], t.dim(), _i64(t.shape),
+                         _i64(t.stride()), stream))
+    return out
+
+
+def Slice(t, ranges):
+    """ops::Slice (src/ops.cpp:158-190): a dense copy of the window [first, second) of every
+    dimension; one (first, second) pair per dimension.  Same checks and messages."""
+    import torch
+    to_tvb, _ = _torch_maps()
+    ranges = list(ranges)
+    if not ranges:
+        raise RuntimeError("Slice ranges cannot be empty")
+    if len(ranges) != t.dim():
+        raise RuntimeError("Slice ranges size must be equal to tensor shape size")
+    for i, (lo, hi) in enumerate(ranges):
+        if lo > hi:
+            raise RuntimeError("first must be less than second")
+        if lo < 0:
+            raise RuntimeError("first must be >= 0 and <= second")
+        if hi > t.shape[i]:
+            raise RuntimeError(f"second must be less than {t.shape[i]}")
+        if lo == hi:
+            raise RuntimeError("Invalid tensor dimension")   # via::calc_numel on the empty result
+    src = t if t.is_contiguous() else contiguous(t)
+    dev, stream = _device_call(src)
+    out = torch.empty([hi - lo for lo, hi in ranges], dtype=t.dtype, device=t.device)
+    check(lib.tvb_slice(dev, src.data_ptr(), out.data_ptr(), to_tvb[t.dtype], src.dim(), _i64(src.shape),
+                        len(ranges), _i64([r[0] for r in ranges]), _i64([r[1] for r in ranges]), stream))
+    return out
+
+
+def Concat(tensors, dim: int):
+    """ops::Concat (src/ops.cpp:1301-1333): tensors that agree in dtype, rank and every extent
+    but `dim`, joined along `dim`.  Same checks and messages (ValueError where the reference
+    throws std::invalid_argument)."""
+    import torch
+    to_tvb, _ = _torch_maps()
+    tensors = list(tensors)
+    if not tensors:
+        raise ValueError("tensors is empty")
+    if len(tensors) == 1:
+        return tensors[0]
+    first = tensors[0]
+    for t in tensors:
+        if t.dtype != first.dtype:
+            raise ValueError("tensors must have same dtype")
+        if t.dim() != first.dim():
+            raise ValueError("tensors must have same number of dimensions")
+        if any(i != dim and t.shape[i] != first.shape[i] for i in range(first.dim())):
+            raise ValueError("tensors must have same shape except concatenation dimension")
+        if t.device != first.device:
+            raise RuntimeError("tensors must live on one device")
+    if not 0 <= dim < first.dim():
+        raise ValueError("concatenation dimension out of range")
+    dense = [t if t.is_contiguous() else contiguous(t) for t in tensors]
+    dev, stream = _device_call(first)
+    shape = list(first.shape)
+    shape[dim] = sum(t.shape[dim] for t in tensors)
+    out = torch.empty(shape, dtype=first.dtype, device=first.device)
+    ptrs = (C.c_void_p * len(dense))(*[t.data_ptr() for t in dense])
+    check(lib.tvb_concat(dev, len(dense), ptrs, out.data_ptr(), to_tvb[first.dtype], first.dim(), _i64(first.shape),
+                         _i64([t.shape[dim] for t in tensors]), dim, stream))
+    return out
+
+
+def Transpose(t):
+    """ops::Transpose of a 2-D tensor (src/ops.cpp:1334-1353), out of place: returns the dense
+    [cols, rows] tensor."""
+    import torch
+    to_tvb, _ = _torch_maps()
+    if t.numel() == 0:
+        raise RuntimeError("tensor a is null")
+    if t.dim() != 2:
+        raise RuntimeError("transpose only support 2D tensor")
+    src = t if t.is_contiguous() else contiguous(t)
+    dev, stream = _device_call(src)
+    out = torch.empty((t.shape[1], t.shape[0]), dtype=t.dtype, device=t.device)
+    check(lib.tvb_transpose2d(dev, src.data_ptr(), out.data_ptr(), to_tvb[t.dtype], t.shape[0], t.shape[1], stream))
+    return out
+
 
 _NP_DTYPES = {INT8: np.int8, INT16: np.int16, INT32: np.int32, INT64: np.int64,
               BFLOAT16: np.uint16, FLOAT16: np.float16, FLOAT32: np.float32, FLOAT64: np.float64}

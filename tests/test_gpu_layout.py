@@ -127,6 +127,9 @@ def test_transpose_2d_matches_the_reference_fixture(dev, dt):
 # Larger and ragged cases against the restatement: every copy kernel, every vector width.
 BIG_VIEWS = [
     # (stored shape, view shape, view strides, offset)
+    ((512, 384), (384, 512), (1, 384), 0),                       # t(), everything 16-byte aligned: vector transpose
+    ((3, 256, 160), (3, 160, 256), (40960, 1, 160), 0),          # permute {0,2,1}, aligned
+    ((200, 144), (144, 200), (1, 144), 0),                       # t(), ragged tiles of whole vectors / words
     ((1000, 777), (777, 1000), (1, 777), 0),                     # t(): tiled transpose, ragged tiles
     ((5, 300, 260), (5, 260, 300), (78000, 1, 260), 0),          # permute {0,2,1}
     ((300, 5, 260), (5, 300, 260), (260, 1300, 1), 0),           # permute {1,0,2}: rows stay contiguous
@@ -201,3 +204,28 @@ def test_argument_checks(dev):
         assert lib.tvb_concat(0, 0, arr, p, R.FLOAT32, 2, i64([4, 4]), i64([4]), 0, None) == 1
     finally:
         dev.free(p)
+
+
+def test_torch_facing_layout_operators(tv):
+    """The Python mirrors of ops::Slice / Concat / Transpose and Tensor::contiguous on torch tensors."""
+    torch = pytest.importorskip("torch")
+    g = torch.Generator(device="cuda").manual_seed(11)
+    x = torch.randint(-100, 100, (6, 40, 56), device="cuda", generator=g, dtype=torch.int32)
+    for view in (x.permute(0, 2, 1), x.permute(2, 0, 1), x[:, 3:29, 8:40], x[1:4], x.transpose(0, 1)[5:20]):
+        assert torch.equal(tv.contiguous(view), view.contiguous())
+    h = x.to(torch.bfloat16)
+    assert torch.equal(tv.Slice(h, [(1, 5), (0, 40), (16, 48)]), h[1:5, :, 16:48])
+    assert torch.equal(tv.Slice(h, [(2, 4), (0, 40), (0, 56)]), h[2:4])
+    assert torch.equal(tv.Concat([h[:2], h[2:3], h[3:]], 0), h)
+    assert torch.equal(tv.Concat([h[:, :, :24], h[:, :, 24:]], 2), h)
+    m = x[0].to(torch.int8)
+    assert torch.equal(tv.Transpose(m), m.t().contiguous())
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="Slice ranges cannot be empty"):
+        tv.Slice(h, [])
+    with pytest.raises(RuntimeError, match="second must be less than 40"):
+        tv.Slice(h, [(0, 1), (0, 41), (0, 1)])
+    with pytest.raises(ValueError, match="same dtype"):
+        tv.Concat([h, x], 0)
+    with pytest.raises(RuntimeError, match="only support 2D"):
+        tv.Transpose(h)
