@@ -61,23 +61,39 @@ struct BoxParams {
 template <typename V>
 __global__ void __launch_bounds__(256)
 strided_copy_kernel(const char* __restrict__ src, char* __restrict__ dst, uint32_t total, const BoxParams p) {
-  const uint32_t stride = gridDim.x * blockDim.x;
-  for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
-    uint32_t rem = idx;
-    int64_t so = 0, dof = 0;
+  // four vectors per thread and trip: all four loads are issued before the first store
+  constexpr int UNROLL = 4;
+  const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x * UNROLL;
+  for (uint64_t base = static_cast<uint64_t>(blockIdx.x) * blockDim.x * UNROLL + threadIdx.x; base < total;
+       base += stride) {
+    V v[UNROLL];
+    int64_t dof[UNROLL];
 #pragma unroll
-    for (int i = kMaxLayoutDims - 1; i >= 1; --i) {
-      if (i < p.ndim) {
-        const uint32_t q = fast_div(rem, p.div[i]);
-        const uint32_t c = rem - q * p.size[i];
-        so += static_cast<int64_t>(c) * p.src_stride[i];
-        dof += static_cast<int64_t>(c) * p.dst_stride[i];
-        rem = q;
+    for (int k = 0; k < UNROLL; ++k) {
+      const uint64_t idx = base + static_cast<uint64_t>(k) * blockDim.x;
+      dof[k] = -1;
+      if (idx < total) {
+        uint32_t rem = static_cast<uint32_t>(idx);
+        int64_t so = 0, d = 0;
+#pragma unroll
+        for (int i = kMaxLayoutDims - 1; i >= 1; --i) {
+          if (i < p.ndim) {
+            const uint32_t q = fast_div(rem, p.div[i]);
+            const uint32_t c = rem - q * p.size[i];
+            so += static_cast<int64_t>(c) * p.src_stride[i];
+            d += static_cast<int64_t>(c) * p.dst_stride[i];
+            rem = q;
+          }
+        }
+        so += static_cast<int64_t>(rem) * p.src_stride[0];
+        d += static_cast<int64_t>(rem) * p.dst_stride[0];
+        v[k] = *reinterpret_cast<const V*>(src + so);
+        dof[k] = d;
       }
     }
-    so += static_cast<int64_t>(rem) * p.src_stride[0];
-    dof += static_cast<int64_t>(rem) * p.dst_stride[0];
-    *reinterpret_cast<V*>(dst + dof) = *reinterpret_cast<const V*>(src + so);
+#pragma unroll
+    for (int k = 0; k < UNROLL; ++k)
+      if (dof[k] >= 0) *reinterpret_cast<V*>(dst + dof[k]) = v[k];
   }
 }
 
@@ -225,20 +241,22 @@ tiled_transpose_words_kernel(const char* __restrict__ src, char* __restrict__ ds
 
 // The transposing copy at full width: 16-byte global accesses on both sides.  Needs every run
 // to start on a 16-byte boundary and to hold whole 16-byte vectors (extents of the two plane
-// indices, all strides and both bases multiples of 16 bytes).  A tile is 128 bytes of u by 128
-// bytes of l.  Each thread loads one 16-byte vector from each of SUB consecutive rows of l,
+// indices, all strides and both bases multiples of 16 bytes).  A tile is 128 bytes of u by
+// LR x 128 bytes of l.  Each thread loads one 16-byte vector from each of SUB consecutive rows of
+// l (LR times),
 // transposes the SUB x SUB blocks of narrow elements in registers, and writes words that hold
 // SUB consecutive values of l into a shared tile whose rows run along l.  That tile is not
 // padded: its 16-byte groups are XOR-swizzled with the source vector index, which makes the
 // word stores of a warp hit 32 different banks and keeps the 16-byte reads of the second
 // phase conflict-free too.
-template <int SUB>
+template <int SUB, int LR>
 __global__ void __launch_bounds__(256)
 tiled_transpose_vec_kernel(const char* __restrict__ src, char* __restrict__ dst, const TransposeParams p) {
   constexpr int ES = 4 / SUB;
-  constexpr int TU = 32 * SUB;   // values of u per tile
-  constexpr int TL = 32 * SUB;   // values of l per tile
-  __shared__ uint4 tile[TU][8];  // [u][32 words along l]
+  constexpr int TU = 32 * SUB;        // values of u per tile
+  constexpr int TL = 32 * SUB * LR;   // values of l per tile: LR groups of SUB rows per thread
+  constexpr int ROW_WORDS = 32 * LR;
+  __shared__ uint4 tile[TU][8 * LR];  // [u][ROW_WORDS words along l]
   uint32_t z = blockIdx.z + p.z0;
   int64_t so = 0, dof = 0;
   for (int i = p.n_outer - 1; i >= 0; --i) {
@@ -252,40 +270,50 @@ tiled_transpose_vec_kernel(const char* __restrict__ src, char* __restrict__ dst,
   char* dbase = dst + dof * ES;
   const int u0 = blockIdx.x * TU, l0 = blockIdx.y * TL;
   {
-    const int uv = threadIdx.x & 7, lg = threadIdx.x >> 3;
-    const int u = u0 + uv * 4 * SUB, l = l0 + lg * SUB;
-    if (u < p.nu && l < p.nl) {
-      uint32_t w[SUB][4];
+    const int uv = threadIdx.x & 7;
+    const int u = u0 + uv * 4 * SUB;
+    uint32_t w[LR][SUB][4];
+    // every load of the thread is issued before the first shared-memory store
 #pragma unroll
-      for (int h = 0; h < SUB; ++h) {
-        const uint4 v = *reinterpret_cast<const uint4*>(sbase + (static_cast<int64_t>(l + h) * p.sl + u) * ES);
-        w[h][0] = v.x; w[h][1] = v.y; w[h][2] = v.z; w[h][3] = v.w;
+    for (int r = 0; r < LR; ++r) {
+      const int l = l0 + ((threadIdx.x >> 3) + 32 * r) * SUB;
+      if (u < p.nu && l < p.nl) {
+#pragma unroll
+        for (int h = 0; h < SUB; ++h) {
+          const uint4 v = *reinterpret_cast<const uint4*>(sbase + (static_cast<int64_t>(l + h) * p.sl + u) * ES);
+          w[r][h][0] = v.x; w[r][h][1] = v.y; w[r][h][2] = v.z; w[r][h][3] = v.w;
+        }
       }
-      uint32_t* t = reinterpret_cast<uint32_t*>(tile);
+    }
+    uint32_t* t = reinterpret_cast<uint32_t*>(tile);
+#pragma unroll
+    for (int r = 0; r < LR; ++r) {
+      const int lg = (threadIdx.x >> 3) + 32 * r;
+      if (!(u < p.nu && l0 + lg * SUB < p.nl)) continue;
       const int col = lg ^ (uv << 2);
 #pragma unroll
       for (int m = 0; m < 4; ++m) {
         const int row = uv * 4 * SUB + m * SUB;
         if constexpr (SUB == 1) {
-          t[row * 32 + col] = w[0][m];
+          t[row * ROW_WORDS + col] = w[r][0][m];
         } else if constexpr (SUB == 2) {
-          t[row * 32 + col] = __byte_perm(w[0][m], w[1][m], 0x5410);
-          t[(row + 1) * 32 + col] = __byte_perm(w[0][m], w[1][m], 0x7632);
+          t[row * ROW_WORDS + col] = __byte_perm(w[r][0][m], w[r][1][m], 0x5410);
+          t[(row + 1) * ROW_WORDS + col] = __byte_perm(w[r][0][m], w[r][1][m], 0x7632);
         } else {
-          const uint32_t t0 = __byte_perm(w[0][m], w[1][m], 0x5140), t1 = __byte_perm(w[2][m], w[3][m], 0x5140);
-          const uint32_t t2 = __byte_perm(w[0][m], w[1][m], 0x7362), t3 = __byte_perm(w[2][m], w[3][m], 0x7362);
-          t[row * 32 + col] = __byte_perm(t0, t1, 0x5410);
-          t[(row + 1) * 32 + col] = __byte_perm(t0, t1, 0x7632);
-          t[(row + 2) * 32 + col] = __byte_perm(t2, t3, 0x5410);
-          t[(row + 3) * 32 + col] = __byte_perm(t2, t3, 0x7632);
+          const uint32_t t0 = __byte_perm(w[r][0][m], w[r][1][m], 0x5140), t1 = __byte_perm(w[r][2][m], w[r][3][m], 0x5140);
+          const uint32_t t2 = __byte_perm(w[r][0][m], w[r][1][m], 0x7362), t3 = __byte_perm(w[r][2][m], w[r][3][m], 0x7362);
+          t[row * ROW_WORDS + col] = __byte_perm(t0, t1, 0x5410);
+          t[(row + 1) * ROW_WORDS + col] = __byte_perm(t0, t1, 0x7632);
+          t[(row + 2) * ROW_WORDS + col] = __byte_perm(t2, t3, 0x5410);
+          t[(row + 3) * ROW_WORDS + col] = __byte_perm(t2, t3, 0x7632);
         }
       }
     }
   }
   __syncthreads();
 #pragma unroll
-  for (int it = threadIdx.x; it < TU * 8; it += 256) {
-    const int c = it & 7, row = it >> 3;
+  for (int it = threadIdx.x; it < TU * 8 * LR; it += 256) {
+    const int c = it % (8 * LR), row = it / (8 * LR);
     const int u = u0 + row, l = l0 + c * 4 * SUB;
     if (u < p.nu && l < p.nl)
       *reinterpret_cast<uint4*>(dbase + (static_cast<int64_t>(u) * p.du + l) * ES) = tile[row][c ^ ((row / (4 * SUB)) & 7)];

@@ -866,13 +866,15 @@ cudaError_t launch_tiled_transpose(const void* src, void* dst, const CopyPlan& p
   if (outer > 0xFFFFFFFFull) return cudaErrorInvalidValue;
   // word tiles: ROWS values of l by UW words of u
   constexpr int ROWS = SUB == 4 ? 128 : 64, UW = 32;
-  constexpr int TILE_U = VEC ? 32 * SUB : SUB ? UW * SUB : TILE, TILE_L = VEC ? 32 * SUB : SUB ? ROWS : TILE;
+  // vector tiles: 128 bytes of u by LR x 128 bytes of l (16 KiB of shared memory for every width)
+  constexpr int LR = SUB == 1 ? 4 : SUB == 2 ? 2 : 1;
+  constexpr int TILE_U = VEC ? 32 * SUB : SUB ? UW * SUB : TILE, TILE_L = VEC ? 32 * SUB * LR : SUB ? ROWS : TILE;
   const unsigned gx = static_cast<unsigned>((tp.nu + TILE_U - 1) / TILE_U), gy = static_cast<unsigned>((tp.nl + TILE_L - 1) / TILE_L);
   for (uint64_t z0 = 0; z0 < outer; z0 += 65535) {
     const unsigned gz = static_cast<unsigned>(outer - z0 < 65535 ? outer - z0 : 65535);
     tp.z0 = static_cast<uint32_t>(z0);
     if constexpr (VEC)
-      tiled_transpose_vec_kernel<SUB><<<dim3(gx, gy, gz), 256, 0, s>>>(static_cast<const char*>(src), static_cast<char*>(dst), tp);
+      tiled_transpose_vec_kernel<SUB, LR><<<dim3(gx, gy, gz), 256, 0, s>>>(static_cast<const char*>(src), static_cast<char*>(dst), tp);
     else if constexpr (SUB != 0)
       tiled_transpose_words_kernel<SUB, ROWS, UW><<<dim3(gx, gy, gz), 256, 0, s>>>(static_cast<const char*>(src), static_cast<char*>(dst), tp);
     else
