@@ -421,6 +421,162 @@ def gpu_arm(args):
     return 0
 
 
+# ---- layout operations (secondary workloads: `--op transpose|permute|slice|concat`) --------------
+# name: (what runs, elements of the source as [rows, cols] or [batch, rows, cols])
+LAYOUT_TEXT = {
+    "transpose": "ops::Transpose of a 2-D tensor [R, C] (tvb_transpose2d)",
+    "permute": "Tensor::permute({0,2,1}).contiguous() of a batched tensor (tvb_repack)",
+    "slice": "ops::Slice: the middle half of the columns of [R, C] (tvb_slice)",
+    "concat": "ops::Concat along dim 1 of [R, 2C/3] and [R, C/3] (tvb_concat)",
+}
+
+
+def layout_arm(args):
+    """One step = one layout operation over tensors resident in HBM; the metric is the algorithmic
+    traffic (every element read once and written once) per second.  Single GPU."""
+    import numpy as np
+    import torch
+
+    torch.cuda.set_device(0)
+    from tensorvia_b200 import _lib, ops
+    lib, check = _lib.lib, _lib.check
+    ops.init(0)
+    es = args.elem_bytes
+    dt = {1: INT8, 2: BF16, 4: F32, 8: 3}[es]
+    R_, C_ = args.rows, args.cols
+    stream = torch.cuda.current_stream().cuda_stream or 1
+    sp = C.c_void_p(stream)
+    i64 = lambda v: (C.c_int64 * len(v))(*[int(x) for x in v])
+
+    def dalloc(n):
+        p = C.c_void_p()
+        check(lib.tvb_malloc(0, n, C.byref(p)))
+        return p.value
+
+    op = args.op
+    if op == "transpose":
+        src_elems, dst_elems = R_ * C_, R_ * C_
+        call = lambda s_, d_: lib.tvb_transpose2d(0, s_, d_, dt, R_, C_, sp)
+        shape_txt = f"[{R_},{C_}] -> [{C_},{R_}]"
+    elif op == "permute":
+        nb, rows = 32, R_ // 32
+        src_elems = dst_elems = nb * rows * C_
+        shape, strides = i64([nb, C_, rows]), i64([rows * C_, 1, C_])
+        call = lambda s_, d_: lib.tvb_repack(0, s_, d_, dt, 3, shape, strides, sp)
+        shape_txt = f"[{nb},{rows},{C_}] viewed as [{nb},{C_},{rows}]"
+    elif op == "slice":
+        src_elems, dst_elems = R_ * C_, R_ * (C_ // 2)
+        shape, b, e = i64([R_, C_]), i64([0, C_ // 4]), i64([R_, C_ // 4 + C_ // 2])
+        call = lambda s_, d_: lib.tvb_slice(0, s_, d_, dt, 2, shape, 2, b, e, sp)
+        shape_txt = f"[{R_},{C_}] -> [{R_},{C_ // 2}]"
+    else:
+        c1 = (2 * C_ // 3) // 16 * 16
+        c2 = C_ - c1
+        src_elems = dst_elems = R_ * C_
+        shape_txt = f"[{R_},{c1}] + [{R_},{c2}] -> [{R_},{C_}]"
+    bytes_algo = (dst_elems * 2) * es        # each output element is read once and written once
+    nsets = max(2, -(-3 * L2_BYTES // ((src_elems + dst_elems) * es)))
+    sets = []
+    for k in range(nsets):
+        ps, pd = dalloc(src_elems * es), dalloc(dst_elems * es)
+        check(lib.tvb_fill_splitmix(0, ps, dt, src_elems, SEED_BASE + 100 + k, 0, 1 if dt in (INT8, 3) else 0, sp))
+        sets.append((ps, pd))
+    if op == "concat":
+        sizes, shp = i64([c1, c2]), i64([R_, c1])
+
+        def call(s_, d_):
+            ptrs = (C.c_void_p * 2)(s_, s_ + R_ * c1 * es)
+            return lib.tvb_concat(0, 2, ptrs, d_, dt, 2, shp, sizes, 1, sp)
+    torch.cuda.synchronize()
+
+    def step(i):
+        ps, pd = sets[i % nsets]
+        check(call(ps, pd))
+
+    for i in range(max(3, args.warmup)):
+        step(i)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(physical_gpu_index(0))
+    sampler.start()
+    launches0 = lib.tvb_kernel_launches()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for i in range(args.steps):
+        step(i)
+    ev1.record()
+    torch.cuda.synchronize()
+    launches = lib.tvb_kernel_launches() - launches0
+    clocks = sampler.stop()
+    check(lib.tvb_sync(0))
+    ms_step = ev0.elapsed_time(ev1) / args.steps
+    gbs = bytes_algo / (ms_step * 1e-3) / 1e9
+
+    # end to end: pinned host source in, operation, pinned host result out
+    hs, hd = C.c_void_p(), C.c_void_p()
+    check(lib.tvb_host_alloc(src_elems * es, C.byref(hs)))
+    check(lib.tvb_host_alloc(dst_elems * es, C.byref(hd)))
+    check(lib.tvb_memcpy_d2h(0, hs, sets[0][0], src_elems * es, None))
+    check(lib.tvb_sync(0))
+    e2e_steps = max(3, min(args.steps, 10))
+    t0 = None
+    for k in range(e2e_steps + 1):
+        if k == 1:
+            t0 = time.perf_counter()
+        check(lib.tvb_memcpy_h2d(0, sets[0][0], hs, src_elems * es, sp))
+        check(call(sets[0][0], sets[0][1]))
+        check(lib.tvb_memcpy_d2h(0, hd, sets[0][1], dst_elems * es, sp))
+        torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    for p_ in (hs, hd):
+        check(lib.tvb_host_free(p_))
+
+    peaks = measured_peaks()
+    line = {
+        "metric": "layout operation GB/s", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": f"u{8 * es}", "data": "synthetic",
+        "config": {"workload": LAYOUT_TEXT[op] + " " + shape_txt, "op": op, "elem_bytes": es,
+                   "l2": f"{nsets} rotating source/destination sets exceed the {L2_BYTES >> 20} MiB L2"},
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
+                     "traffic": None, "peak_source": f"{peaks['source']}: hbm_gbs", "bytes_per_launch": bytes_algo},
+        "e2e": {"value": bytes_algo / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": src_elems * es,
+                "d2h_bytes_per_step": dst_elems * es, "ms_per_step": e2e_ms, "steps": e2e_steps,
+                "api": "tvb_memcpy_h2d + the operation + tvb_memcpy_d2h (pinned host buffers)"},
+        "gpu_launches": int(launches), "clocks": clocks,
+    }
+    if not args.no_cpu_baseline:
+        try:
+            sys.path.insert(0, str(ROOT / "tests"))
+            import refcheck as R
+            use_all_host_threads()
+            rows = min(R_, 4096)
+            x = R.fill((rows, C_), dt, 1, 1 if dt in (INT8, 3) else 0)
+            have = R.have_ref()
+            t0 = time.perf_counter()
+            if op == "transpose":
+                (R.ref_transpose2d(x, dt) if have else R.oracle_transpose(x))
+            elif op == "permute":
+                x3 = x.reshape(32, rows // 32, C_)
+                (R.ref_permute_contiguous(x3, dt, (0, 2, 1)) if have else
+                 R.oracle_repack(x3, (32, C_, rows // 32), (rows // 32 * C_, 1, C_)))
+            elif op == "slice":
+                b_, e_ = [0, C_ // 4], [rows, C_ // 4 + C_ // 2]
+                (R.ref_slice(x, dt, b_, e_) if have else R.oracle_slice(x, b_, e_))
+            else:
+                parts = [np.ascontiguousarray(x[:, :c1]), np.ascontiguousarray(x[:, c1:])]
+                t0 = time.perf_counter()
+                (R.ref_concat(parts, dt, 1) if have else R.oracle_concat(parts, 1))
+            t = time.perf_counter() - t0
+            frac = (rows / R_)
+            line["cpu_baseline"] = {"value": bytes_algo * frac / t / 1e9, "unit": "GB/s", "cores": os.cpu_count() if op == "transpose" else 1,
+                                    "kind": "reference" if have else "port",
+                                    "sample": f"first {rows} of {R_} rows, 1 run, {t:.2f} s (includes the harness's copy of the result)"}
+        except Exception as e:
+            line["cpu_baseline"] = {"value": None, "unit": "GB/s", "cores": 0, "kind": "unavailable", "sample": str(e)[:200]}
+    emit(line)
+    return 0
+
+
 class OneLineStdout:
     """Routes file descriptor 1 to stderr while the benchmark runs (NCCL, the reference library
     and others print banners to stdout) and hands back the real stdout for the one JSON line."""
@@ -461,6 +617,11 @@ def main():
     ap.add_argument("--config", default="c2", choices=sorted(CONFIGS))
     ap.add_argument("--impl", default="tensorvia_b200", choices=["tensorvia_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--op", default="matmul", choices=["matmul", "transpose", "permute", "slice", "concat"],
+                    help="matmul (default, the headline workload) or one of the layout operations either side of it")
+    ap.add_argument("--rows", type=int, default=16384, help="layout operations: rows of the source")
+    ap.add_argument("--cols", type=int, default=16384, help="layout operations: columns of the source")
+    ap.add_argument("--elem-bytes", type=int, default=2, choices=[1, 2, 4, 8], help="layout operations: element size")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="weak (default): one full problem per GPU; strong: one problem, rows or batches split over the GPUs")
     args = ap.parse_args()
@@ -472,6 +633,8 @@ def main():
     with OneLineStdout() as OUT:
         if args.impl == "reference":
             return reference_arm(args)
+        if args.op != "matmul":
+            return layout_arm(args)
         return gpu_arm(args)
 
 
