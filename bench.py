@@ -260,6 +260,11 @@ def gpu_arm(args):
     # exceed the L2 and no step finds its operands cached from the previous one.
     per_set = bytes_a + bytes_b + bytes_c
     nsets = max(2, -(-3 * L2_BYTES // per_set)) if per_set < 3 * L2_BYTES else 1
+    if world > 1:
+        # shards may differ by a tile row; every rank must make the same number of broadcasts below
+        t = torch.tensor([nsets], device="cuda", dtype=torch.int64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        nsets = int(t[0])
     stream = torch.cuda.current_stream().cuda_stream or 1   # 1 = CUDA's handle of the legacy default stream
     sp = C.c_void_p(stream)
 
@@ -289,9 +294,45 @@ def gpu_arm(args):
 
     dtc = lib.tvb_compute_type(dt, dt)
 
+    # ---- optional gather of the row shards on rank 0 (strong scaling, 2-D problems) -----------
+    gather = args.gather if (strong and batch is None) else "none"
+    shared_base, gather_bufs = None, None
+    if gather != "none":
+        counts = [ops.shard_range(CONFIGS[cfg_name][3], 128, world, r)[1] for r in range(world)]
+        full_rows = sum(counts)
+    if gather == "fused":
+        # rank 0 owns the whole C; every rank maps it and its GEMM epilogue stores into it over NVLink
+        handle, base = _lib.IpcHandle(), C.c_void_p()
+        blob = torch.zeros(C.sizeof(_lib.IpcHandle), dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            check(lib.tvb_shared_alloc(local, full_rows * N * es, C.byref(base), C.byref(handle)))
+            blob.copy_(torch.tensor(list(bytes(handle)), dtype=torch.uint8))
+        dist.broadcast(blob, src=0)
+        if rank != 0:
+            C.memmove(C.byref(handle), bytes(blob.cpu().tolist()), C.sizeof(_lib.IpcHandle))
+            check(lib.tvb_shared_open(local, C.byref(handle), C.byref(base)))
+        shared_base = base.value
+    elif gather == "nccl":
+        tdt = {F32: torch.float32, BF16: torch.bfloat16, F16: torch.float16, INT8: torch.int8}[dt]
+        c_local = torch.empty((M, N), dtype=tdt, device="cuda")
+        gather_bufs = [torch.empty((n_, N), dtype=tdt, device="cuda") for n_ in counts] if rank == 0 else None
+
     def step(i):
         pa, pb, pc = sets[i % nsets]
-        check(lib.tvb_matmul(local, pa, pb, pc, dt, dt, dtc, nb, M, K, N, sp))
+        if gather == "fused":
+            check(lib.tvb_matmul(local, pa, pb, shared_base + begin * N * es, dt, dt, dtc, nb, M, K, N, sp))
+        elif gather == "nccl":
+            check(lib.tvb_matmul(local, pa, pb, c_local.data_ptr(), dt, dt, dtc, nb, M, K, N, sp))
+            # gather of unequal slabs: point-to-point sends to rank 0 (what dist.gather does underneath)
+            if rank == 0:
+                gather_bufs[0].copy_(c_local)
+                ops_ = [dist.P2POp(dist.irecv, gather_bufs[r], r) for r in range(1, world)]
+            else:
+                ops_ = [dist.P2POp(dist.isend, c_local, 0)]
+            for w in dist.batch_isend_irecv(ops_):
+                w.wait()
+        else:
+            check(lib.tvb_matmul(local, pa, pb, pc, dt, dt, dtc, nb, M, K, N, sp))
 
     for i in range(max(3, args.warmup)):
         step(i)
@@ -392,6 +433,8 @@ def gpu_arm(args):
                 "kernel": f"tcgen05 {info.tile_m}x{info.tile_n}x{info.tile_k}, {info.stages} stages, {info.ctas} CTAs, {info.passes} pass(es)" if info.algo == 1 else "simt",
                 "l2": f"{nsets} rotating operand sets ({nsets * per_set >> 20} MiB) exceed the {L2_BYTES >> 20} MiB L2",
                 "inputs": "SplitMix64 counter-based, seeds 0x5EED0000+2*cfg (A), +1 (B)",
+                "gather": {"none": "none: C stays sharded", "nccl": "C slabs sent to rank 0 over NCCL after each product, inside the timed region",
+                           "fused": "every rank's GEMM epilogue stores its C tiles into rank 0's buffer over NVLink (peer stores), inside the timed region"}[gather],
             },
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
                          "traffic": NCU_TRAFFIC_BYTES.get(cfg_name), "peak_source": f"{peaks['source']}: {peak_name}",
@@ -622,6 +665,8 @@ def main():
     ap.add_argument("--rows", type=int, default=16384, help="layout operations: rows of the source")
     ap.add_argument("--cols", type=int, default=16384, help="layout operations: columns of the source")
     ap.add_argument("--elem-bytes", type=int, default=2, choices=[1, 2, 4, 8], help="layout operations: element size")
+    ap.add_argument("--gather", default="none", choices=["none", "nccl", "fused"],
+                    help="with --scaling strong on a 2-D problem: also bring the whole C to rank 0 in every step")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="weak (default): one full problem per GPU; strong: one problem, rows or batches split over the GPUs")
     args = ap.parse_args()

@@ -116,6 +116,25 @@ int tvb_memcpy_h2d(int device, void* dst, const void* src, size_t bytes, void* s
 int tvb_memcpy_d2h(int device, void* dst, const void* src, size_t bytes, void* stream);
 int tvb_memcpy_d2d(int device, void* dst, const void* src, size_t bytes, void* stream);
 
+/* ---- buffers other processes' GPUs can write: the gather fused into the GEMM ---------
+ * (No counterpart in the reference, which is single-device.)  With one process per GPU, the
+ * rank that wants the whole row-sharded result allocates it with tvb_shared_alloc and sends
+ * the 72-byte handle to the other ranks (any channel: a store, a broadcast); they map it with
+ * tvb_shared_open and pass `mapped pointer + their row offset` as C to tvb_matmul.  The
+ * epilogue's ordinary 16-byte stores then land in the owner's memory over NVLink while the
+ * tensor cores work on the next tile: no staging copy, no separate gather.  Once every rank
+ * has synchronised its stream (and the ranks have met at a host barrier) the owner's buffer
+ * holds the full result.  Only plain peer stores are used: no multicast, no peer loads.
+ * tvb_shared_open fails with TVB_ERR_UNSUPPORTED when the two GPUs have no peer access. */
+typedef struct tvb_ipc_handle {
+  unsigned char reserved[64];
+  uint64_t bytes;               /* size of the buffer */
+} tvb_ipc_handle;
+int tvb_shared_alloc(int device, size_t bytes, void** ptr, tvb_ipc_handle* handle);
+int tvb_shared_free(int device, void* ptr);
+int tvb_shared_open(int device, const tvb_ipc_handle* handle, void** ptr);
+int tvb_shared_close(int device, void* ptr);
+
 /* ---- layout operations either side of the matmul -------------------------------------
  * Byte movers, each one pass at memory speed: every element is read once and written once.
  * All take dense device buffers unless said otherwise, extents and strides in ELEMENTS of

@@ -40,6 +40,10 @@ class PlanInfo(C.Structure):
                 ("workspace_bytes", C.c_uint64), ("tiles", C.c_uint64)]
 
 
+class IpcHandle(C.Structure):
+    _fields_ = [("reserved", C.c_ubyte * 64), ("bytes", C.c_uint64)]
+
+
 class TvbError(RuntimeError):
     def __init__(self, code: int, message: str):
         super().__init__(f"{ERR_NAMES.get(code, code)}: {message}")
@@ -69,6 +73,10 @@ SIGNATURES = {
     "tvb_matmul_algo": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _i64, _vp, _i]),
     "tvb_matmul_strided": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _i64,
                                 C.POINTER(_i64), C.POINTER(_i64), _vp, _i]),
+    "tvb_shared_alloc": (_i, [_i, _sz, C.POINTER(_vp), C.POINTER(IpcHandle)]),
+    "tvb_shared_free": (_i, [_i, _vp]),
+    "tvb_shared_open": (_i, [_i, C.POINTER(IpcHandle), C.POINTER(_vp)]),
+    "tvb_shared_close": (_i, [_i, _vp]),
     "tvb_repack": (_i, [_i, _vp, _vp, _i, _i, C.POINTER(_i64), C.POINTER(_i64), _vp]),
     "tvb_slice": (_i, [_i, _vp, _vp, _i, _i, C.POINTER(_i64), _i, C.POINTER(_i64), C.POINTER(_i64), _vp]),
     "tvb_concat": (_i, [_i, _i, C.POINTER(_vp), _vp, _i, _i, C.POINTER(_i64), C.POINTER(_i64), _i, _vp]),

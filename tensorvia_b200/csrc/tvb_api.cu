@@ -13,6 +13,7 @@
 #include <cstring>
 #include <mutex>
 #include <string>
+#include <vector>
 
 #include "aux_kernels.cuh"
 #include "block_pool.h"
@@ -130,6 +131,26 @@ bool valid_dtype(int d) { return d >= 0 && d <= 7; }
 size_t dtype_size(int d) {
   static const size_t s[8] = {1, 2, 4, 8, 2, 2, 4, 8};
   return valid_dtype(d) ? s[d] : 0;
+}
+
+// ------------------------------------------------------------------------------------
+// buffers of other GPUs mapped into this process (tvb_shared_open)
+// ------------------------------------------------------------------------------------
+struct PeerMapping {
+  uintptr_t base;
+  size_t bytes;
+};
+std::mutex g_peer_mu;
+std::vector<PeerMapping> g_peer_maps;
+std::atomic<int> g_peer_count{0};
+
+bool is_peer_mapping(const void* p) {
+  if (g_peer_count.load(std::memory_order_acquire) == 0) return false;
+  const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+  std::lock_guard<std::mutex> g(g_peer_mu);
+  for (const PeerMapping& m : g_peer_maps)
+    if (a >= m.base && a < m.base + m.bytes) return true;
+  return false;
 }
 
 // ------------------------------------------------------------------------------------
@@ -511,6 +532,12 @@ int run_umma(Context* c, const UmmaPlan& plan, int dta, int dtb, const Operand& 
   auto round_up = [](size_t v, size_t m) { return (v + m - 1) / m * m; };
   const size_t vec = 16 / es;                                   // elements per 16 bytes
   const bool c_vec = (N * es) % 16 == 0 && !misaligned(C);
+  // A C in another GPU's memory (a buffer mapped with tvb_shared_open): the epilogue then writes
+  // whole rows, which cross NVLink as few large writes instead of many 16-byte ones (measured on
+  // 2 GPUs, C5 row shards written into rank 0: 5.13 ms with 16-byte stores, 4.29 ms with row
+  // stores, against 4.29 ms without any gather and 5.11 ms with an NCCL gather afterwards).
+  bool c_remote = is_peer_mapping(C);
+  if (getenv("TVB_FORCE_ROW_STORES")) c_remote = true;   // lets a single GPU exercise that epilogue
 
   // What the kernel is given for one operand: where it starts, whether the contraction index
   // is its contiguous one (K-major) or the other (MN-major), the elements between consecutive
@@ -695,7 +722,7 @@ int run_umma(Context* c, const UmmaPlan& plan, int dta, int dtb, const Operand& 
   p.partial = nullptr;
   p.flags = c->d_flags;
   p.C = C;
-  p.c_vec = c_vec ? 1 : 0;
+  p.c_vec = c_vec ? (c_remote ? 2 : 1) : 0;
   p.status = c->d_status;
   p.wait_limit_ns = static_cast<uint64_t>(g_wait_limit_ms.load()) * 1000000ull;
   const int grid = static_cast<int>(p.total_tiles < static_cast<uint32_t>(c->sm_count) ? p.total_tiles
@@ -1174,6 +1201,87 @@ int tvb_pool_trim(int device) {
   DeviceGuard guard(device);
   TVB_CUDA(cudaStreamSynchronize(c->stream));
   c->pool->trim();
+  return TVB_OK;
+}
+
+int tvb_shared_alloc(int device, size_t bytes, void** ptr, tvb_ipc_handle* handle) {
+  Context* c = nullptr;
+  int rc = get_ctx(device, &c);
+  if (rc != TVB_OK) return rc;
+  if (!ptr || !handle || bytes == 0) return fail(TVB_ERR_INVALID_ARG, "ptr and handle must not be null, bytes > 0");
+  static_assert(sizeof(cudaIpcMemHandle_t) <= sizeof(tvb_ipc_handle), "handle size");
+  DeviceGuard guard(device);
+  void* p = nullptr;
+  // a whole allocation of its own (not a pool block): the handle names an allocation's base
+  cudaError_t e = cudaMalloc(&p, bytes);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(TVB_ERR_OOM, "out of device memory for %zu shared bytes", bytes);
+  }
+  cudaIpcMemHandle_t h;
+  e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    cudaFree(p);
+    return fail(TVB_ERR_CUDA, "cudaIpcGetMemHandle failed: %s", cudaGetErrorString(e));
+  }
+  std::memset(handle, 0, sizeof(*handle));
+  std::memcpy(handle->reserved, &h, sizeof(h));
+  handle->bytes = bytes;
+  *ptr = p;
+  return TVB_OK;
+}
+
+int tvb_shared_free(int device, void* ptr) {
+  Context* c = nullptr;
+  int rc = get_ctx(device, &c);
+  if (rc != TVB_OK) return rc;
+  if (!ptr) return TVB_OK;
+  DeviceGuard guard(device);
+  TVB_CUDA(cudaFree(ptr));
+  return TVB_OK;
+}
+
+int tvb_shared_open(int device, const tvb_ipc_handle* handle, void** ptr) {
+  Context* c = nullptr;
+  int rc = get_ctx(device, &c);
+  if (rc != TVB_OK) return rc;
+  if (!handle || !ptr) return fail(TVB_ERR_INVALID_ARG, "handle and ptr must not be null");
+  DeviceGuard guard(device);
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle->reserved, sizeof(h));
+  void* p = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(e == cudaErrorPeerAccessUnsupported ? TVB_ERR_UNSUPPORTED : TVB_ERR_CUDA,
+                "cudaIpcOpenMemHandle failed: %s", cudaGetErrorString(e));
+  }
+  {
+    std::lock_guard<std::mutex> g(g_peer_mu);
+    g_peer_maps.push_back(PeerMapping{reinterpret_cast<uintptr_t>(p), static_cast<size_t>(handle->bytes)});
+    g_peer_count.store(static_cast<int>(g_peer_maps.size()), std::memory_order_release);
+  }
+  *ptr = p;
+  return TVB_OK;
+}
+
+int tvb_shared_close(int device, void* ptr) {
+  Context* c = nullptr;
+  int rc = get_ctx(device, &c);
+  if (rc != TVB_OK) return rc;
+  if (!ptr) return TVB_OK;
+  DeviceGuard guard(device);
+  {
+    std::lock_guard<std::mutex> g(g_peer_mu);
+    for (size_t i = 0; i < g_peer_maps.size(); ++i)
+      if (g_peer_maps[i].base == reinterpret_cast<uintptr_t>(ptr)) {
+        g_peer_maps.erase(g_peer_maps.begin() + static_cast<long>(i));
+        break;
+      }
+    g_peer_count.store(static_cast<int>(g_peer_maps.size()), std::memory_order_release);
+  }
+  TVB_CUDA(cudaIpcCloseMemHandle(ptr));
   return TVB_OK;
 }
 

@@ -96,7 +96,8 @@ struct UmmaGemmParams {
   uint32_t* partial;     // [tile - split_from][part - 1][cta rank][64 column groups of 16 B][128 rows] of 32-bit sums
   uint32_t* flags;       // [tile - split_from][part - 1][cta rank][row quarter]
   void* C;
-  int32_t c_vec;         // rows of C start on 16-byte boundaries: 16-byte stores, else element stores
+  int32_t c_vec;         // 1: rows of C start on 16-byte boundaries, 16-byte stores; 0: element stores through the
+                         // staging area; 2: aligned rows in another GPU's memory, whole-row stores through the staging area
   uint32_t* status;
   uint64_t wait_limit_ns;
 };
@@ -231,6 +232,63 @@ __device__ __forceinline__ void store_block_staged(uint32_t* stage, const uint32
       else if constexpr (OP == OP_F16) *d = __float2half_rn(__uint_as_float(x));
       else if constexpr (OP == OP_BF16) *d = __float2bfloat16_rn(__uint_as_float(x));
       else *d = static_cast<int8_t>(x & 0xFFu);
+    }
+  }
+  __syncwarp();
+}
+
+// The same staging for a C whose rows ARE 16-byte aligned but which lies in another GPU's
+// memory: there the 16-byte stores of store_row_chunk, 32 rows per instruction, cross NVLink as
+// 32 small writes, while whole rows of 128 bytes travel as one.  Two 32-column blocks of 1- or
+// 2-byte results are packed into 32-bit words first (64 columns = 32 words of f16/bf16, 16
+// words of int8), so that every store instruction writes 128 contiguous bytes of one row
+// (int8: 64 bytes of each of two rows).
+template <int OP>
+__device__ __forceinline__ void store_pair_packed(uint32_t* stage, const uint32_t (&v0)[32], const uint32_t (&v1)[32],
+                                                  typename OpTraits<OP>::Out* c_batch, int ldc, int row0, int col,
+                                                  int M, int N, int lane) {
+  constexpr int ES = OpTraits<OP>::ES;
+  static_assert(ES == 1 || ES == 2, "4-byte results already fill a word each");
+  auto pack16 = [](uint32_t a, uint32_t b) -> uint32_t {
+    if constexpr (OP == OP_F16) {
+      const __half2 h = __floats2half2_rn(__uint_as_float(a), __uint_as_float(b));
+      return *reinterpret_cast<const uint32_t*>(&h);
+    } else {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(a), __uint_as_float(b));
+      return *reinterpret_cast<const uint32_t*>(&h);
+    }
+  };
+  char* const cbytes = reinterpret_cast<char*>(c_batch);
+  if constexpr (ES == 2) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      stage[lane * 33 + j] = pack16(v0[2 * j], v0[2 * j + 1]);
+      stage[lane * 33 + 16 + j] = pack16(v1[2 * j], v1[2 * j + 1]);
+    }
+    __syncwarp();
+    const bool col_ok = col + 2 * lane < N;   // N is even here: whole words
+#pragma unroll 4
+    for (int r = 0; r < 32; ++r) {
+      const uint32_t x = stage[r * 33 + lane];
+      if (col_ok && row0 + r < M)
+        *reinterpret_cast<uint32_t*>(cbytes + (static_cast<size_t>(row0 + r) * ldc + col + 2 * lane) * 2) = x;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      stage[lane * 33 + j] = (v0[4 * j] & 0xFFu) | ((v0[4 * j + 1] & 0xFFu) << 8) | ((v0[4 * j + 2] & 0xFFu) << 16) |
+                             (v0[4 * j + 3] << 24);
+      stage[lane * 33 + 8 + j] = (v1[4 * j] & 0xFFu) | ((v1[4 * j + 1] & 0xFFu) << 8) |
+                                 ((v1[4 * j + 2] & 0xFFu) << 16) | (v1[4 * j + 3] << 24);
+    }
+    __syncwarp();
+    const int w = lane & 15, half = lane >> 4;
+    const bool col_ok = col + 4 * w < N;      // N is a multiple of 16 here: whole words
+#pragma unroll 4
+    for (int r = 0; r < 32; r += 2) {
+      const uint32_t x = stage[(r + half) * 33 + w];
+      if (col_ok && row0 + r + half < M)
+        *reinterpret_cast<uint32_t*>(cbytes + static_cast<size_t>(row0 + r + half) * ldc + col + 4 * w) = x;
     }
   }
   __syncwarp();
@@ -438,15 +496,19 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
           ptx::tmem_ld_32x32(taddr + c * 64 + 32, v1);
           ptx::tmem_ld_wait();
           const int cols_left = p.N - (col0 + c * 64);
-          if (p.c_vec != 0) {
+          if (p.c_vec == 1) {
             if (row < p.M && cols_left > 0) store_row_chunk<OP>(crow + c * 64, v0, cols_left);
             if (row < p.M && cols_left > 32) store_row_chunk<OP>(crow + c * 64 + 32, v1, cols_left - 32);
           } else {
             uint32_t* st = staging + (warp - 2) * kStageWords;
             Out* cb = Cbase + static_cast<size_t>(b) * p.M * p.N;
             const int row0 = mt * BLOCK_M + quad * 32;
-            store_block_staged<OP>(st, v0, cb, p.N, row0, col0 + c * 64, p.M, p.N, lane);
-            store_block_staged<OP>(st, v1, cb, p.N, row0, col0 + c * 64 + 32, p.M, p.N, lane);
+            if (p.c_vec == 2 && OP != OP_TF32) {
+              store_pair_packed<OP>(st, v0, v1, cb, p.N, row0, col0 + c * 64, p.M, p.N, lane);
+            } else {
+              store_block_staged<OP>(st, v0, cb, p.N, row0, col0 + c * 64, p.M, p.N, lane);
+              store_block_staged<OP>(st, v1, cb, p.N, row0, col0 + c * 64 + 32, p.M, p.N, lane);
+            }
           }
         }
         ptx::tc_fence_before();
@@ -492,7 +554,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
         if (row < p.M) {
           float* cf = reinterpret_cast<float*>(Cbase) +
                       (static_cast<size_t>(b) * p.M + static_cast<size_t>(row)) * p.N + col0;
-          if (p.c_vec != 0) {
+          if (p.c_vec == 1) {
             float4* crow = reinterpret_cast<float4*>(cf);
 #pragma unroll
             for (int g = 0; g < HALF_N / 4; ++g)
@@ -500,7 +562,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
                 crow[g] = make_float4(acc[4 * g], acc[4 * g + 1], acc[4 * g + 2], acc[4 * g + 3]);
           }
         }
-        if (p.c_vec == 0) {
+        if (p.c_vec != 1) {
           uint32_t* st = staging + (warp - 2) * kStageWords;
           float* cb = reinterpret_cast<float*>(Cbase) + static_cast<size_t>(b) * p.M * p.N;
           const int row0 = mt * BLOCK_M + quad * 32;

@@ -369,15 +369,19 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_con
               }
             }
             const int cols_left = p.N - (col0 + c * 64);
-            if (p.c_vec != 0) {
+            if (p.c_vec == 1) {
               if (row < p.M && cols_left > 0) store_row_chunk<OP>(crow + c * 64, v0, cols_left);
               if (row < p.M && cols_left > 32) store_row_chunk<OP>(crow + c * 64 + 32, v1, cols_left - 32);
             } else {
               uint32_t* st = staging + (warp - 2) * kStageWords;
               Out* cb = Cbase + static_cast<size_t>(b) * p.M * p.N;
               const int row0 = row - lane;
-              store_block_staged<OP>(st, v0, cb, p.N, row0, col0 + c * 64, p.M, p.N, lane);
-              store_block_staged<OP>(st, v1, cb, p.N, row0, col0 + c * 64 + 32, p.M, p.N, lane);
+              if (p.c_vec == 2 && OP != OP_TF32) {
+                store_pair_packed<OP>(st, v0, v1, cb, p.N, row0, col0 + c * 64, p.M, p.N, lane);
+              } else {
+                store_block_staged<OP>(st, v0, cb, p.N, row0, col0 + c * 64, p.M, p.N, lane);
+                store_block_staged<OP>(st, v1, cb, p.N, row0, col0 + c * 64 + 32, p.M, p.N, lane);
+              }
             }
           }
         }
@@ -466,7 +470,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_con
         if (row < p.M) {
           float* cf = reinterpret_cast<float*>(Cbase) +
                       (static_cast<size_t>(b) * p.M + static_cast<size_t>(row)) * p.N + col0;
-          if (p.c_vec != 0) {
+          if (p.c_vec == 1) {
             float4* crow = reinterpret_cast<float4*>(cf);
 #pragma unroll
             for (int g = 0; g < HALF_N / 4; ++g)
@@ -474,7 +478,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_con
                 crow[g] = make_float4(acc[4 * g], acc[4 * g + 1], acc[4 * g + 2], acc[4 * g + 3]);
           }
         }
-        if (p.c_vec == 0) {
+        if (p.c_vec != 1) {
           uint32_t* st = staging + (warp - 2) * kStageWords;
           float* cb = reinterpret_cast<float*>(Cbase) + static_cast<size_t>(b) * p.M * p.N;
 #pragma unroll

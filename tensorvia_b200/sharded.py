@@ -13,6 +13,11 @@ rows a single GPU would produce.  The only collectives are optional and outside 
 compute: `broadcast_b` (B from one rank to all, once) and `gather_result` (all-gather of
 the C slabs when one rank wants the whole result).  torch.distributed carries them (NCCL
 on GPUs, gloo in the CPU tests).
+
+`GatheredResult` is the fused form of that gather for one rank that wants the whole result:
+the owner's buffer is mapped into every rank's address space (CUDA IPC) and each rank's GEMM
+writes its C tiles straight into it over NVLink from the epilogue, so there is no gather
+step after the compute at all.
 """
 from __future__ import annotations
 
@@ -96,3 +101,96 @@ def sharded_matmul(a_local, b_local, shard: Shard, world: int, *, gather: bool =
         n_tail = (a_local.shape[1], b_local.shape[2]) if shard.axis == "batch" else (b_local.shape[1],)
         c_local = torch.zeros((0,) + tuple(n_tail), dtype=b_local.dtype, device=b_local.device)
     return gather_result(c_local, shard, world, group=group)
+
+
+class _RawCuda:
+    """Lets torch wrap a raw device pointer without copying (the CUDA array interface)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class GatheredResult:
+    """The whole C of a row- or batch-sharded product, living on `owner`, written by every
+    rank's GEMM epilogue directly (peer stores over NVLink; no multicast, no peer loads).
+
+    Collective: every rank of `group` constructs it with the same arguments, and calls
+    `matmul_into` and `finish` the same number of times.  `tensor` is the full result on the
+    owner (None elsewhere), valid after `finish`.
+    """
+
+    def __init__(self, shape_a, shape_b, dtype_a, dtype_b, world: int, rank: int, owner: int = 0, group=None):
+        import ctypes as C
+
+        import torch
+        import torch.distributed as dist
+        from . import _lib
+        self._lib, self._dist, self._group = _lib, dist, group
+        self.world, self.rank, self.owner = world, rank, owner
+        to_tvb, from_tvb = ops._torch_maps()
+        self.dta, self.dtb = to_tvb[dtype_a], to_tvb[dtype_b]
+        self.dtc = ops.compute_type(self.dta, self.dtb)
+        self.batch, self.M, self.K, self.N = ops.check_shapes(tuple(shape_a), tuple(shape_b))
+        self.shard = plan(shape_a, shape_b, world, rank)
+        self.shape_c = (self.batch, self.M, self.N) if len(shape_a) == 3 else (self.M, self.N)
+        es = ops.dtype_size(self.dtc)
+        self.nbytes = es * self.batch * self.M * self.N
+        # bytes from the start of C to this rank's first row (2-D) or batch (3-D)
+        self.offset = es * self.shard.begin * (self.N if self.shard.axis == "rows" else self.M * self.N)
+        self.device = torch.cuda.current_device()
+        ops.init(self.device)
+        handle = _lib.IpcHandle()
+        base = C.c_void_p()
+        blob = torch.zeros(C.sizeof(_lib.IpcHandle), dtype=torch.uint8, device="cuda")
+        if rank == owner:
+            _lib.check(_lib.lib.tvb_shared_alloc(self.device, self.nbytes, C.byref(base), C.byref(handle)))
+            blob.copy_(torch.tensor(list(bytes(handle)), dtype=torch.uint8))
+        dist.broadcast(blob, src=owner, group=group)     # the handle travels once
+        if rank != owner:
+            C.memmove(C.byref(handle), bytes(blob.cpu().tolist()), C.sizeof(_lib.IpcHandle))
+            _lib.check(_lib.lib.tvb_shared_open(self.device, C.byref(handle), C.byref(base)))
+        self.base = base.value
+        self.tensor = None
+        if rank == owner:
+            raw = torch.as_tensor(_RawCuda(self.base, self.nbytes), device="cuda")
+            self.tensor = raw.view(from_tvb[self.dtc]).reshape(self.shape_c)
+
+    def matmul_into(self, a_local, b_local):
+        """This rank's shard of the product, written into the owner's buffer; asynchronous on
+        torch's current stream."""
+        import ctypes as C
+
+        import torch
+        if self.shard.count == 0:
+            return
+        if not a_local.is_contiguous() or not b_local.is_contiguous():
+            raise RuntimeError("shards must be contiguous")
+        stream = torch.cuda.current_stream().cuda_stream or 1
+        if self.shard.axis == "rows":
+            nb, m = 1, self.shard.count
+        else:
+            nb, m = self.shard.count, self.M
+        self._lib.check(self._lib.lib.tvb_matmul(self.device, a_local.data_ptr(), b_local.data_ptr(),
+                                                 self.base + self.offset, self.dta, self.dtb, self.dtc, nb, m,
+                                                 self.K, self.N, C.c_void_p(stream)))
+
+    def finish(self):
+        """Waits for this rank's stores, then for every rank: after it the owner holds all of C."""
+        import torch
+        torch.cuda.current_stream().synchronize()
+        self._dist.barrier(group=self._group)
+        return self.tensor
+
+    def close(self):
+        """Collective: unmaps (peers) or frees (owner) the buffer; `tensor` must not be used after."""
+        if self.base is None:
+            return
+        self._dist.barrier(group=self._group)      # nobody still writes
+        self.tensor = None
+        if self.rank == self.owner:
+            self._dist.barrier(group=self._group)  # peers unmap first
+            self._lib.check(self._lib.lib.tvb_shared_free(self.device, self.base))
+        else:
+            self._lib.check(self._lib.lib.tvb_shared_close(self.device, self.base))
+            self._dist.barrier(group=self._group)
+        self.base = None

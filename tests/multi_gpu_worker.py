@@ -1,6 +1,7 @@
 """Worker of tests/test_multi_gpu.py: one rank per GPU under torch.distributed.run (NCCL).
 Shards a matmul by rows (2-D) or batches (3-D), broadcasts B from rank 0 once, multiplies the
-local shard with the CUDA operator, all-gathers C and compares with the unsharded product."""
+local shard with the CUDA operator, all-gathers C and compares with the unsharded product; then
+repeats the product with the gather fused into the epilogue (peer stores into rank 0's buffer)."""
 import os
 import sys
 from pathlib import Path
@@ -48,6 +49,23 @@ def main():
         ok = ok and good
         if rank == 0:
             print(f"{dt} {sa} @ {sb}: shard axis {shard.axis}, gathered {tuple(full.shape)}, match={good}", flush=True)
+        # the same gather fused into the GEMM: every rank's epilogue stores into rank 0's buffer
+        gathered = sharded.GatheredResult(sa, sb, dt, dt, world, rank, owner=0)
+        for _ in range(2):      # the buffer is reusable
+            gathered.matmul_into(a_loc, b_loc)
+            whole = gathered.finish()
+        if rank == 0:
+            # each rank ran the kernel the unsharded problem's rows would run: bit-equal rows for
+            # integers; floats may differ in the last bit where the tile plan differs
+            if dt == torch.int8:
+                fused_ok = bool((whole == want).all())
+            else:
+                err = (torch.linalg.norm(whole.double() - want.double()) / torch.linalg.norm(want.double())).item()
+                fused_ok = err <= (1e-5 if dt == torch.float32 else 1e-2) and whole.shape == want.shape
+            fused_ok = fused_ok and bool((whole == full).all())
+            print(f"{dt} fused gather: fused_match={fused_ok}", flush=True)
+            ok = ok and fused_ok
+        gathered.close()
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     dist.barrier()

@@ -267,3 +267,23 @@ def test_shared_tiles_fp32(dev, tv, monkeypatch):
     c3, _ = dev.matmul(A, R.FLOAT32, B, R.FLOAT32, algo=TCGEN05)
     assert_matches(c3, dtc, exp, dte, what="fp32 whole tiles")
     assert R.rel_frobenius(c1, c3, R.FLOAT32) < 1e-5
+
+
+@pytest.mark.parametrize("dt", [R.BFLOAT16, R.FLOAT16, R.INT8, R.FLOAT32])
+def test_whole_row_stores_of_the_peer_memory_epilogue(dev, dt, monkeypatch):
+    """The epilogue used when C lies in another GPU's memory (whole rows through the staging area
+    instead of 16-byte stores), forced on one GPU: same results bit for bit."""
+    F = 0 if dt >= R.BFLOAT16 else 1
+    for (M, K, N) in ((300, 256, 528), (128, 64, 96), (513, 200, 1040), (64, 512, 256)):
+        A = R.fill((M, K), dt, 31, F); B = R.fill((K, N), dt, 32, F)
+        monkeypatch.delenv("TVB_FORCE_ROW_STORES", raising=False)
+        want, _ = dev.matmul(A, dt, B, dt)
+        monkeypatch.setenv("TVB_FORCE_ROW_STORES", "1")
+        got, _ = dev.matmul(A, dt, B, dt)
+        assert got.tobytes() == want.tobytes(), (M, K, N)
+    A = R.fill((3, 140, 96), dt, 33, F); B = R.fill((3, 96, 160), dt, 34, F)
+    monkeypatch.delenv("TVB_FORCE_ROW_STORES", raising=False)
+    want, _ = dev.matmul(A, dt, B, dt)
+    monkeypatch.setenv("TVB_FORCE_ROW_STORES", "1")
+    got, _ = dev.matmul(A, dt, B, dt)
+    assert got.tobytes() == want.tobytes()

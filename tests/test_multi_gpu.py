@@ -20,4 +20,5 @@ def test_row_and_batch_shards_gather_to_the_unsharded_product(tv):
                           "--master-addr", "127.0.0.1", "--master-port", "29577", str(worker)],
                          capture_output=True, text=True, timeout=600, env=env)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
-    assert out.stdout.count("match=True") == 4
+    assert out.stdout.count(" match=True") == 4
+    assert out.stdout.count("fused_match=True") == 4
