@@ -471,6 +471,7 @@ LAYOUT_TEXT = {
     "permute": "Tensor::permute({0,2,1}).contiguous() of a batched tensor (tvb_repack)",
     "slice": "ops::Slice: the middle half of the columns of [R, C] (tvb_slice)",
     "concat": "ops::Concat along dim 1 of [R, 2C/3] and [R, C/3] (tvb_concat)",
+    "typecast": "ops::Typecast bfloat16 -> float32 (tvb_typecast), the widening the reference's CPU matmul applies to half operands",
 }
 
 
@@ -512,16 +513,22 @@ def layout_arm(args):
         shape, b, e = i64([R_, C_]), i64([0, C_ // 4]), i64([R_, C_ // 4 + C_ // 2])
         call = lambda s_, d_: lib.tvb_slice(0, s_, d_, dt, 2, shape, 2, b, e, sp)
         shape_txt = f"[{R_},{C_}] -> [{R_},{C_ // 2}]"
+    elif op == "typecast":
+        es, dt = 2, BF16                      # source bf16, destination fp32
+        src_elems = dst_elems = R_ * C_
+        call = lambda s_, d_: lib.tvb_typecast(0, s_, d_, BF16, F32, R_ * C_, sp)
+        shape_txt = f"[{R_},{C_}]"
     else:
         c1 = (2 * C_ // 3) // 16 * 16
         c2 = C_ - c1
         src_elems = dst_elems = R_ * C_
         shape_txt = f"[{R_},{c1}] + [{R_},{c2}] -> [{R_},{C_}]"
-    bytes_algo = (dst_elems * 2) * es        # each output element is read once and written once
-    nsets = max(2, -(-3 * L2_BYTES // ((src_elems + dst_elems) * es)))
+    des = 4 if op == "typecast" else es       # bytes per destination element
+    bytes_algo = dst_elems * (es + des)       # each output element is read once and written once
+    nsets = max(2, -(-3 * L2_BYTES // (src_elems * es + dst_elems * des)))
     sets = []
     for k in range(nsets):
-        ps, pd = dalloc(src_elems * es), dalloc(dst_elems * es)
+        ps, pd = dalloc(src_elems * es), dalloc(dst_elems * des)
         check(lib.tvb_fill_splitmix(0, ps, dt, src_elems, SEED_BASE + 100 + k, 0, 1 if dt in (INT8, 3) else 0, sp))
         sets.append((ps, pd))
     if op == "concat":
@@ -557,7 +564,7 @@ def layout_arm(args):
     # end to end: pinned host source in, operation, pinned host result out
     hs, hd = C.c_void_p(), C.c_void_p()
     check(lib.tvb_host_alloc(src_elems * es, C.byref(hs)))
-    check(lib.tvb_host_alloc(dst_elems * es, C.byref(hd)))
+    check(lib.tvb_host_alloc(dst_elems * des, C.byref(hd)))
     check(lib.tvb_memcpy_d2h(0, hs, sets[0][0], src_elems * es, None))
     check(lib.tvb_sync(0))
     e2e_steps = max(3, min(args.steps, 10))
@@ -567,7 +574,7 @@ def layout_arm(args):
             t0 = time.perf_counter()
         check(lib.tvb_memcpy_h2d(0, sets[0][0], hs, src_elems * es, sp))
         check(call(sets[0][0], sets[0][1]))
-        check(lib.tvb_memcpy_d2h(0, hd, sets[0][1], dst_elems * es, sp))
+        check(lib.tvb_memcpy_d2h(0, hd, sets[0][1], dst_elems * des, sp))
         torch.cuda.synchronize()
     e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
     for p_ in (hs, hd):
@@ -583,7 +590,7 @@ def layout_arm(args):
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
                      "traffic": None, "peak_source": f"{peaks['source']}: hbm_gbs", "bytes_per_launch": bytes_algo},
         "e2e": {"value": bytes_algo / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": src_elems * es,
-                "d2h_bytes_per_step": dst_elems * es, "ms_per_step": e2e_ms, "steps": e2e_steps,
+                "d2h_bytes_per_step": dst_elems * des, "ms_per_step": e2e_ms, "steps": e2e_steps,
                 "api": "tvb_memcpy_h2d + the operation + tvb_memcpy_d2h (pinned host buffers)"},
         "gpu_launches": int(launches), "clocks": clocks,
     }
@@ -605,6 +612,8 @@ def layout_arm(args):
             elif op == "slice":
                 b_, e_ = [0, C_ // 4], [rows, C_ // 4 + C_ // 2]
                 (R.ref_slice(x, dt, b_, e_) if have else R.oracle_slice(x, b_, e_))
+            elif op == "typecast":
+                (R.ref_typecast(x, BF16, F32) if have else R.oracle_typecast(x, BF16, F32))
             else:
                 parts = [np.ascontiguousarray(x[:, :c1]), np.ascontiguousarray(x[:, c1:])]
                 t0 = time.perf_counter()
@@ -660,7 +669,7 @@ def main():
     ap.add_argument("--config", default="c2", choices=sorted(CONFIGS))
     ap.add_argument("--impl", default="tensorvia_b200", choices=["tensorvia_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--op", default="matmul", choices=["matmul", "transpose", "permute", "slice", "concat"],
+    ap.add_argument("--op", default="matmul", choices=["matmul", "transpose", "permute", "slice", "concat", "typecast"],
                     help="matmul (default, the headline workload) or one of the layout operations either side of it")
     ap.add_argument("--rows", type=int, default=16384, help="layout operations: rows of the source")
     ap.add_argument("--cols", type=int, default=16384, help="layout operations: columns of the source")

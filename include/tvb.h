@@ -168,6 +168,15 @@ int tvb_concat(int device, int count, const void* const* srcs, void* dst, int dt
 int tvb_transpose2d(int device, const void* src, void* dst, int dtype, int64_t rows, int64_t cols,
                     void* stream);
 
+/* ops::Typecast (src/ops.cpp:1277-1300 -> TypecastImpl<Device::CUDA>::execute,
+ * src/backend/cuda/typecast.cu:6-82): dst[i] = static_cast<dst type>(src[i]) for `count` elements
+ * of dense buffers; float -> half / bfloat16 rounds to nearest even, half <-> bfloat16 go through
+ * float, float -> integer truncates toward zero.  Only the casts the reference allows
+ * (valid_casts, include/core/type_traits.h:237-260, and the identity) are accepted; the others
+ * return TVB_ERR_DTYPE with the reference's message "Invalid typecast from X to Y". */
+int tvb_typecast(int device, const void* src, void* dst, int src_dtype, int dst_dtype,
+                 uint64_t count, void* stream);
+
 /* ---- dtype rules -----------------------------------------------------------------*/
 /* via::compute_type (include/core/type_traits.h:270-287); -1 for a bad dtype. */
 int tvb_compute_type(int dtype_a, int dtype_b);

@@ -174,6 +174,16 @@ int tvref_transpose2d(const void* data, int dtype, int64_t rows, int64_t cols, v
   });
 }
 
+// ops::Typecast(const Tensor&, DataType)  (src/ops.cpp:1277-1300)
+int tvref_typecast(const void* data, int dtype, int rank, const int64_t* dims, int dst_dtype, void* out,
+                   uint64_t out_bytes) {
+  return guarded([&] {
+    Tensor t(const_cast<void*>(data), shape_of(rank, dims), static_cast<via::DataType>(dtype), via::Device::CPU);
+    Tensor c = ops::Typecast(std::as_const(t), static_cast<via::DataType>(dst_dtype));
+    return emit(c, out, out_bytes, nullptr);
+  });
+}
+
 // ops::Mul(a.t()-style views made contiguous): a and b are given with their STORED shapes and a
 // permutation each; the product is Mul(a.permute(pa).contiguous(), b.permute(pb).contiguous()).
 int tvref_mul_permuted(const void* a, int dtype_a, int rank, const int64_t* dims_a, const int64_t* perm_a,

@@ -14,6 +14,6 @@ __all__ = ["ops", "matmul", "Mul", "matmul_host", "sharded"]
 def __getattr__(name):
     if name in ("ops", "_lib", "sharded"):
         return importlib.import_module(f"{__name__}.{name}")
-    if name in ("matmul", "Mul", "matmul_host", "contiguous", "Slice", "Concat", "Transpose"):
+    if name in ("matmul", "Mul", "matmul_host", "contiguous", "Slice", "Concat", "Transpose", "Typecast"):
         return getattr(importlib.import_module(f"{__name__}.ops"), name)
     raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

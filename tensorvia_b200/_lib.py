@@ -77,6 +77,7 @@ SIGNATURES = {
     "tvb_shared_free": (_i, [_i, _vp]),
     "tvb_shared_open": (_i, [_i, C.POINTER(IpcHandle), C.POINTER(_vp)]),
     "tvb_shared_close": (_i, [_i, _vp]),
+    "tvb_typecast": (_i, [_i, _vp, _vp, _i, _i, _u64, _vp]),
     "tvb_repack": (_i, [_i, _vp, _vp, _i, _i, C.POINTER(_i64), C.POINTER(_i64), _vp]),
     "tvb_slice": (_i, [_i, _vp, _vp, _i, _i, C.POINTER(_i64), _i, C.POINTER(_i64), C.POINTER(_i64), _vp]),
     "tvb_concat": (_i, [_i, _i, C.POINTER(_vp), _vp, _i, _i, C.POINTER(_i64), C.POINTER(_i64), _i, _vp]),

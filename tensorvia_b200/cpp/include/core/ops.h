@@ -31,6 +31,11 @@ Tensor Concat(const std::vector<Tensor>& tensors, int dim);
 // In-place transpose of a 2-D tensor (src/ops.cpp:1334-1353): the storage is rewritten.
 void Transpose(Tensor& a);
 
+// A dense copy of `a` converted to `dst_type`: the casts, the refusal ("Invalid typecast from X to
+// Y") and the rounding of the reference's ops::Typecast (src/ops.cpp:1277-1300,
+// src/backend/cuda/typecast.cu:6-27).  A tensor already of that type is returned as a copy.
+Tensor Typecast(const Tensor& a, via::DataType dst_type);
+
 Tensor Zeros(const std::vector<int64_t>& shape, via::DataType dtype);
 Tensor Ones(const std::vector<int64_t>& shape, via::DataType dtype);
 Tensor Fill(const std::vector<int64_t>& shape, via::DataType dtype, float value);

@@ -1,5 +1,5 @@
-// ops::Slice, ops::Concat and ops::Transpose over the C ABI (reference front ends:
-// src/ops.cpp:158-190, 1301-1353; CUDA back ends: src/backend/cuda/slice.cu, concat.cu,
+// ops::Slice, ops::Concat, ops::Transpose and ops::Typecast over the C ABI (reference front ends:
+// src/ops.cpp:158-190, 1277-1353; CUDA back ends: src/backend/cuda/slice.cu, concat.cu,
 // transpose.cu).  Host tensors make the round trip through the GPU, as in ops::Mul.
 #include <format>
 #include <string>
@@ -111,6 +111,26 @@ void Transpose(Tensor& a) {
   Tensor res = tvhost::adopt({cols, rows}, a.dtype(), out, Device::CUDA);
   if (host) res.to_host();
   a = std::move(res);
+}
+
+Tensor Typecast(const Tensor& a, DataType dst_type) {
+  if (a.data() == nullptr || a.numel() == 0) throw std::runtime_error("tensor a is null");
+  static const char* names[8] = {"int8", "int16", "int32", "int64", "bfloat16", "float16", "float32", "float64"};
+  if (a.dtype() == dst_type) return a;
+  const bool host = a.device() == Device::CPU;
+  Tensor src = dense_on_device(a);
+  auto ss = cuda_storage(src);
+  auto out = std::make_shared<tvhost::CudaStorage>(nullptr, src.numel(), dst_type, ss->cuda());
+  const int rc = tvb_typecast(ss->cuda()->device(), src.data(), out->data(), static_cast<int>(a.dtype()),
+                              static_cast<int>(dst_type), src.numel(), nullptr);
+  if (rc == TVB_ERR_DTYPE)
+    throw std::runtime_error(std::format("Invalid typecast from {} to {}", names[static_cast<int>(a.dtype())],
+                                         names[static_cast<int>(dst_type)]));
+  tvhost::check(rc, "tvb_typecast");
+  ss->cuda()->wait();
+  Tensor res = tvhost::adopt(src.shape(), dst_type, out, Device::CUDA);
+  if (host) res.to_host();
+  return res;
 }
 
 }  // namespace ops

@@ -211,6 +211,30 @@ int main() {
     Tensor rows = A.slice({{8, 12}}).contiguous();
     EXPECT(rows.at<float>({0, 0}) == A.at<float>({8, 0}) && rows.at<float>({3, 31}) == A.at<float>({11, 31}));
   }
+  // ---- Typecast ---------------------------------------------------------------------------------
+  {
+    std::vector<float> hv = {1.5f, -2.75f, 300.9f, -0.4f, 65504.f, 1e-8f};
+    Tensor f(hv.data(), {2, 3}, DataType::FLOAT32, Device::CUDA);
+    Tensor i = ops::Typecast(f, DataType::INT32);
+    EXPECT(i.dtype() == DataType::INT32 && i.at<int32_t>({0, 0}) == 1 && i.at<int32_t>({0, 1}) == -2 &&
+           i.at<int32_t>({0, 2}) == 300 && i.at<int32_t>({1, 0}) == 0);
+    Tensor h = ops::Typecast(f, DataType::FLOAT16);
+    Tensor back = ops::Typecast(h, DataType::FLOAT32);
+    EXPECT(back.at<float>({0, 0}) == 1.5f && back.at<float>({0, 1}) == -2.75f && back.at<float>({0, 2}) == 301.0f &&
+           back.at<float>({1, 1}) == 65504.f);
+    Tensor b = ops::Typecast(h, DataType::BFLOAT16);
+    EXPECT(float(b.at<bfloat16>({0, 0})) == 1.5f && float(b.at<bfloat16>({0, 2})) == 300.0f);   // 301 ties to even
+    EXPECT(thrown([&] { ops::Typecast(f, DataType::INT8); }) == "Invalid typecast from float32 to int8");
+    EXPECT(thrown([&] { ops::Typecast(i, DataType::FLOAT16); }) == "Invalid typecast from int32 to float16");
+    // casting both operands first equals the mixed-dtype product
+    Tensor a8 = Tensor::Random({24, 16}, -10, 10, DataType::INT8), bh = Tensor::Random({16, 8}, -1, 1, DataType::FLOAT16);
+    Tensor mixed = ops::Mul(a8, bh);
+    Tensor cast = ops::Mul(ops::Typecast(a8, DataType::FLOAT32), ops::Typecast(bh, DataType::FLOAT32));
+    bool close = mixed.dtype() == DataType::FLOAT32;
+    for (int r = 0; r < 24; ++r)
+      for (int c = 0; c < 8; ++c) close = close && std::fabs(mixed.at<float>({r, c}) - cast.at<float>({r, c})) <= 1e-4f;
+    EXPECT(close);
+  }
   std::printf(g_failed ? "%d check(s) failed\n" : "api_check: all checks passed\n", g_failed);
   return g_failed ? 1 : 0;
 }

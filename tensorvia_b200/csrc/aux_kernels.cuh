@@ -140,6 +140,52 @@ split_tf32_transpose_kernel(const T* __restrict__ src, float* __restrict__ hi,
   }
 }
 
+// ---- ops::Typecast ---------------------------------------------------------------------------
+// One element converted as the reference's cast_cuda does (src/backend/cuda/typecast.cu:6-27):
+// static_cast between the C types; float -> half / bfloat16 round to nearest even; half <->
+// bfloat16 through float; float -> integer truncates toward zero.
+template <typename S, typename D>
+__device__ __forceinline__ D cast_elem(S x) {
+  if constexpr (std::is_same_v<S, D>) return x;
+  else if constexpr (std::is_same_v<S, __half> && std::is_same_v<D, __nv_bfloat16>) return __float2bfloat16_rn(__half2float(x));
+  else if constexpr (std::is_same_v<S, __nv_bfloat16> && std::is_same_v<D, __half>) return __float2half_rn(__bfloat162float(x));
+  else if constexpr (std::is_same_v<S, __half>) return static_cast<D>(__half2float(x));
+  else if constexpr (std::is_same_v<S, __nv_bfloat16>) return static_cast<D>(__bfloat162float(x));
+  else if constexpr (std::is_same_v<D, __half>) return __float2half_rn(static_cast<float>(x));
+  else if constexpr (std::is_same_v<D, __nv_bfloat16>) return __float2bfloat16_rn(static_cast<float>(x));
+  else return static_cast<D>(x);
+}
+
+template <typename T, int N>
+struct alignas(sizeof(T) * N) ElemPack {
+  T v[N];
+};
+
+// HBM-bound: count * (sizeof(S) + sizeof(D)) bytes.  Eight elements per thread and trip, moved as
+// aligned packs (8 to 64 bytes a side) when `vec` says both pointers allow it; the tail and
+// unaligned buffers go element by element.
+template <typename S, typename D>
+static __global__ void __launch_bounds__(256)
+typecast_kernel(const S* __restrict__ src, D* __restrict__ dst, size_t n, int vec) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  const size_t tid = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  size_t done = 0;
+  if (vec) {
+    const size_t packs = n / 8;
+    const ElemPack<S, 8>* sp = reinterpret_cast<const ElemPack<S, 8>*>(src);
+    ElemPack<D, 8>* dp = reinterpret_cast<ElemPack<D, 8>*>(dst);
+    for (size_t i = tid; i < packs; i += stride) {
+      const ElemPack<S, 8> in = sp[i];
+      ElemPack<D, 8> out;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) out.v[j] = cast_elem<S, D>(in.v[j]);
+      dp[i] = out;
+    }
+    done = packs * 8;
+  }
+  for (size_t i = done + tid; i < n; i += stride) dst[i] = cast_elem<S, D>(src[i]);
+}
+
 // ---- seeded counter-based fill --------------------------------------------------------
 // Element i takes the (first_index + i)-th output of SplitMix64 seeded with `seed`
 // (state_j = seed + (j+1) * 0x9E3779B97F4A7C15, then the standard finaliser).

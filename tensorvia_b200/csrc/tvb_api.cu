@@ -981,6 +981,85 @@ int copy_box(Context* c, const void* src, void* dst, size_t es, const LayoutDim*
   return TVB_OK;
 }
 
+// ------------------------------------------------------------------------------------
+// ops::Typecast
+// ------------------------------------------------------------------------------------
+// valid_casts of the reference (include/core/type_traits.h:237-260) plus the identity
+bool cast_valid(int s, int d) {
+  static const int ok[22][2] = {
+      {TVB_INT8, TVB_FLOAT32},     {TVB_INT16, TVB_FLOAT32},    {TVB_INT16, TVB_FLOAT64},   {TVB_INT32, TVB_FLOAT32},
+      {TVB_INT32, TVB_FLOAT64},    {TVB_INT64, TVB_FLOAT64},    {TVB_FLOAT32, TVB_FLOAT16}, {TVB_FLOAT32, TVB_INT32},
+      {TVB_FLOAT32, TVB_INT64},    {TVB_INT8, TVB_INT16},       {TVB_INT8, TVB_INT32},      {TVB_INT8, TVB_INT64},
+      {TVB_INT16, TVB_INT32},      {TVB_INT32, TVB_INT64},      {TVB_FLOAT16, TVB_FLOAT32}, {TVB_FLOAT16, TVB_FLOAT64},
+      {TVB_FLOAT16, TVB_BFLOAT16}, {TVB_BFLOAT16, TVB_FLOAT32}, {TVB_BFLOAT16, TVB_FLOAT64}, {TVB_BFLOAT16, TVB_FLOAT16},
+      {TVB_FLOAT32, TVB_FLOAT64},  {TVB_FLOAT64, TVB_FLOAT32}};
+  if (s == d) return true;
+  for (const auto& p : ok)
+    if (p[0] == s && p[1] == d) return true;
+  return false;
+}
+
+template <typename S, typename D>
+cudaError_t launch_typecast(const void* src, void* dst, size_t n, int sm_count, cudaStream_t s) {
+  const bool vec = reinterpret_cast<uintptr_t>(src) % (sizeof(S) * 8) == 0 && reinterpret_cast<uintptr_t>(dst) % (sizeof(D) * 8) == 0;
+  size_t blocks = (n / 8 + 255) / 256;
+  const size_t cap = static_cast<size_t>(sm_count) * 16;
+  if (blocks > cap) blocks = cap;
+  if (blocks == 0) blocks = 1;
+  typecast_kernel<S, D><<<static_cast<unsigned>(blocks), 256, 0, s>>>(static_cast<const S*>(src), static_cast<D*>(dst), n,
+                                                                      vec ? 1 : 0);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError();
+}
+
+template <typename S>
+cudaError_t typecast_from(int ddt, const void* src, void* dst, size_t n, int sm, cudaStream_t s) {
+  // only the destinations valid_casts allows for S are instantiated
+  if constexpr (std::is_same_v<S, int8_t>) {
+    switch (ddt) {
+      case TVB_INT16: return launch_typecast<S, int16_t>(src, dst, n, sm, s);
+      case TVB_INT32: return launch_typecast<S, int32_t>(src, dst, n, sm, s);
+      case TVB_INT64: return launch_typecast<S, int64_t>(src, dst, n, sm, s);
+      default: return launch_typecast<S, float>(src, dst, n, sm, s);
+    }
+  } else if constexpr (std::is_same_v<S, int16_t>) {
+    switch (ddt) {
+      case TVB_INT32: return launch_typecast<S, int32_t>(src, dst, n, sm, s);
+      case TVB_FLOAT32: return launch_typecast<S, float>(src, dst, n, sm, s);
+      default: return launch_typecast<S, double>(src, dst, n, sm, s);
+    }
+  } else if constexpr (std::is_same_v<S, int32_t>) {
+    switch (ddt) {
+      case TVB_INT64: return launch_typecast<S, int64_t>(src, dst, n, sm, s);
+      case TVB_FLOAT32: return launch_typecast<S, float>(src, dst, n, sm, s);
+      default: return launch_typecast<S, double>(src, dst, n, sm, s);
+    }
+  } else if constexpr (std::is_same_v<S, int64_t>) {
+    return launch_typecast<S, double>(src, dst, n, sm, s);
+  } else if constexpr (std::is_same_v<S, __nv_bfloat16>) {
+    switch (ddt) {
+      case TVB_FLOAT16: return launch_typecast<S, __half>(src, dst, n, sm, s);
+      case TVB_FLOAT32: return launch_typecast<S, float>(src, dst, n, sm, s);
+      default: return launch_typecast<S, double>(src, dst, n, sm, s);
+    }
+  } else if constexpr (std::is_same_v<S, __half>) {
+    switch (ddt) {
+      case TVB_BFLOAT16: return launch_typecast<S, __nv_bfloat16>(src, dst, n, sm, s);
+      case TVB_FLOAT32: return launch_typecast<S, float>(src, dst, n, sm, s);
+      default: return launch_typecast<S, double>(src, dst, n, sm, s);
+    }
+  } else if constexpr (std::is_same_v<S, float>) {
+    switch (ddt) {
+      case TVB_FLOAT16: return launch_typecast<S, __half>(src, dst, n, sm, s);
+      case TVB_INT32: return launch_typecast<S, int32_t>(src, dst, n, sm, s);
+      case TVB_INT64: return launch_typecast<S, int64_t>(src, dst, n, sm, s);
+      default: return launch_typecast<S, double>(src, dst, n, sm, s);
+    }
+  } else {
+    return launch_typecast<S, float>(src, dst, n, sm, s);
+  }
+}
+
 int layout_prologue(int device, const void* src, void* dst, int dtype, int ndim, Context** c) {
   int rc = get_ctx(device, c);
   if (rc != TVB_OK) return rc;
@@ -1590,6 +1669,37 @@ int tvb_concat(int device, int count, const void* const* srcs, void* dst, int dt
 int tvb_transpose2d(int device, const void* src, void* dst, int dtype, int64_t rows, int64_t cols, void* stream) {
   const int64_t shape[2] = {cols, rows}, strides[2] = {1, cols};
   return tvb_repack(device, src, dst, dtype, 2, shape, strides, stream);
+}
+
+int tvb_typecast(int device, const void* src, void* dst, int src_dtype, int dst_dtype, uint64_t count, void* stream) {
+  Context* c = nullptr;
+  int rc = get_ctx(device, &c);
+  if (rc != TVB_OK) return rc;
+  if (!src || !dst || count == 0) return fail(TVB_ERR_INVALID_ARG, "tensor a is null");
+  if (!valid_dtype(src_dtype) || !valid_dtype(dst_dtype)) return fail(TVB_ERR_DTYPE, "dtype out of range: %d, %d", src_dtype, dst_dtype);
+  static const char* names[8] = {"int8", "int16", "int32", "int64", "bfloat16", "float16", "float32", "float64"};
+  if (!cast_valid(src_dtype, dst_dtype))
+    return fail(TVB_ERR_DTYPE, "Invalid typecast from %s to %s", names[src_dtype], names[dst_dtype]);
+  DeviceGuard guard(device);
+  cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : c->stream;
+  if (src_dtype == dst_dtype) {
+    TVB_CUDA(cudaMemcpyAsync(dst, src, count * dtype_size(src_dtype), cudaMemcpyDeviceToDevice, s));
+    return TVB_OK;
+  }
+  cudaError_t e;
+  const size_t n = static_cast<size_t>(count);
+  switch (src_dtype) {
+    case TVB_INT8: e = typecast_from<int8_t>(dst_dtype, src, dst, n, c->sm_count, s); break;
+    case TVB_INT16: e = typecast_from<int16_t>(dst_dtype, src, dst, n, c->sm_count, s); break;
+    case TVB_INT32: e = typecast_from<int32_t>(dst_dtype, src, dst, n, c->sm_count, s); break;
+    case TVB_INT64: e = typecast_from<int64_t>(dst_dtype, src, dst, n, c->sm_count, s); break;
+    case TVB_BFLOAT16: e = typecast_from<__nv_bfloat16>(dst_dtype, src, dst, n, c->sm_count, s); break;
+    case TVB_FLOAT16: e = typecast_from<__half>(dst_dtype, src, dst, n, c->sm_count, s); break;
+    case TVB_FLOAT32: e = typecast_from<float>(dst_dtype, src, dst, n, c->sm_count, s); break;
+    default: e = typecast_from<double>(dst_dtype, src, dst, n, c->sm_count, s); break;
+  }
+  if (e != cudaSuccess) return fail(TVB_ERR_CUDA, "typecast launch failed: %s", cudaGetErrorString(e));
+  return TVB_OK;
 }
 
 int tvb_shard_range(int64_t units, int64_t granule, int parts, int index, int64_t* begin, int64_t* count) {

@@ -225,6 +225,25 @@ def Transpose(t):
     return out
 
 
+def Typecast(t, dst_dtype):
+    """ops::Typecast (src/ops.cpp:1277-1300): a dense copy of `t` converted to `dst_dtype` (a torch
+    dtype or a Tensorvia dtype number).  Only the casts the reference allows; the others raise
+    RuntimeError("Invalid typecast from X to Y")."""
+    import torch
+    to_tvb, from_tvb = _torch_maps()
+    ddt = to_tvb[dst_dtype] if isinstance(dst_dtype, torch.dtype) else int(dst_dtype)
+    if t.numel() == 0:
+        raise RuntimeError("tensor a is null")
+    src = t if t.is_contiguous() else contiguous(t)
+    dev, stream = _device_call(src)
+    out = torch.empty(tuple(t.shape), dtype=from_tvb[ddt], device=t.device)
+    rc = lib.tvb_typecast(dev, src.data_ptr(), out.data_ptr(), to_tvb[t.dtype], ddt, src.numel(), stream)
+    if rc == 3:   # TVB_ERR_DTYPE: the reference throws std::runtime_error with this message
+        raise RuntimeError(lib.tvb_last_error_string().decode())
+    check(rc)
+    return out
+
+
 _NP_DTYPES = {INT8: np.int8, INT16: np.int16, INT32: np.int32, INT64: np.int64,
               BFLOAT16: np.uint16, FLOAT16: np.float16, FLOAT32: np.float32, FLOAT64: np.float64}
 

@@ -12,8 +12,9 @@ so the pin is the reference's implementation run here on seeded inputs:
                       and a SHA-256 of the whole result
   golden_configs.npz  sampled rows of the five benchmark configurations at FULL size
   golden_layout.npz   the layout operations either side of the matmul: permute().contiguous(),
-                      ops::Slice, slice().contiguous(), ops::Concat, ops::Transpose, and ops::Mul of
-                      permuted views made contiguous
+                      ops::Slice, slice().contiguous(), ops::Concat, ops::Transpose, ops::Mul of
+                      permuted views made contiguous, and ops::Typecast (the casts it allows, its
+                      refusals with their messages)
   golden_meta.json    compute_type table, the messages ops::Mul throws for bad shapes
                       (src/ops.cpp:540-556), thread count, sizes
 
@@ -168,7 +169,8 @@ SHAPE_CASES = [((2, 3), (4, 5)), ((2, 3), (3,)), ((2, 3, 4), (3, 4, 5)), ((2, 3,
 
 
 # ---- layout operations: views made contiguous, slices, concatenation, views multiplied ----------
-from layout_cases import CONCAT_CASES, LAYOUT_DTYPES, MUL_VIEW_CASES, PERMUTE_CASES, SLICE_CASES, pins_view_route  # noqa: E402
+from layout_cases import (CONCAT_CASES, LAYOUT_DTYPES, MUL_VIEW_CASES, PERMUTE_CASES, SLICE_CASES,  # noqa: E402
+                          pinned_casts, pins_view_route, typecast_input)
 
 
 def layout():
@@ -191,6 +193,16 @@ def layout():
         c, dtc = R.ref_mul_permuted(R.fill(sa, dt, 900 + i, F(dt)), dt, pa, R.fill(sb, dt, 950 + i, F(dt)), dt, pb)
         out[f"mulview_{i}"] = c
         out[f"mulview_{i}_dt"] = np.int32(dtc)
+    for sdt, ddt in pinned_casts():
+        out[f"cast_{sdt}_{ddt}"] = R.ref_typecast(typecast_input(sdt), sdt, ddt)
+    rejected = []
+    for sdt in range(8):
+        for ddt in range(8):
+            try:
+                R.ref_typecast(typecast_input(sdt, 8), sdt, ddt)
+            except RuntimeError as e:
+                rejected.append(f"{sdt}>{ddt}:{e}")
+    out["cast_rejected"] = np.array(rejected)
     np.savez_compressed(HERE / "golden_layout.npz", **out)
 
 

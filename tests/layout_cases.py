@@ -21,3 +21,28 @@ def pins_view_route(shape, begin, end) -> bool:
     """Tensor::slice(...).contiguous() is pinned only where the view is not a leading-dimension
     slice: there the reference drops the view's offset (see oracle/layout_oracle.c)."""
     return any(lo != 0 or hi != n for lo, hi, n in list(zip(begin, end, shape))[1:])
+
+
+def typecast_input(sdt: int, n: int = 4099):
+    """Seeded source values for the typecast cases: integers in [-10, 10]; floats spread over
+    [-300, 300) so that float -> integer truncation and half rounding are exercised."""
+    import numpy as np
+    import refcheck as R
+    if sdt <= INT64:
+        return R.fill((n,), sdt, 970 + sdt, 1)
+    x = R.to_f64(R.fill((n,), FLOAT32, 970 + sdt), FLOAT32) * 300.0
+    if sdt == FLOAT32:
+        return x.astype(np.float32)
+    if sdt == FLOAT16:
+        return x.astype(np.float16)
+    if sdt == BFLOAT16:
+        return R.f32_to_bf16_bits(x.astype(np.float32))
+    return x + 1e-9 * x   # float64: values that are not exactly representable in float32
+
+
+# the casts whose reference HOST arithmetic is sound (everything but float16 -> bfloat16, where the
+# reference's bfloat16_t(float) constructor zeroes normal values)
+def pinned_casts():
+    import refcheck as R
+    return [(s, d) for s in range(8) for d in range(8)
+            if s != d and R.oracle_cast_valid(s, d) and not (s == FLOAT16 and d == BFLOAT16)]

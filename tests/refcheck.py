@@ -34,7 +34,7 @@ SEED_BASE = 0x5EED0000
 
 
 def build_oracle() -> Path:
-    newest = max((ORACLE_DIR / f).stat().st_mtime for f in ("matmul_oracle.c", "layout_oracle.c"))
+    newest = max((ORACLE_DIR / f).stat().st_mtime for f in ("matmul_oracle.c", "layout_oracle.c", "typecast_oracle.c"))
     if not ORACLE_LIB.exists() or ORACLE_LIB.stat().st_mtime < newest:
         subprocess.run(["make", "-C", str(ORACLE_DIR), "oracle"], check=True, capture_output=True)
     return ORACLE_LIB
@@ -102,6 +102,7 @@ def ref() -> C.CDLL:
         lib.tvref_slice.argtypes = [vp, i, i, i64p, i, i64p, i64p, vp, u64, i64p]
         lib.tvref_concat.argtypes = [i, C.POINTER(vp), i, i, i64p, i, vp, u64, i64p]
         lib.tvref_transpose2d.argtypes = [vp, i, C.c_int64, C.c_int64, vp, u64, i64p]
+        lib.tvref_typecast.argtypes = [vp, i, i, i64p, i, vp, u64]
         lib.tvref_mul_permuted.argtypes = [vp, i, i, i64p, i64p, vp, i, i64p, i64p, vp, u64, C.POINTER(i), i64p]
         _ref = lib
     return _ref
@@ -364,3 +365,28 @@ def ref_mul_permuted(a: np.ndarray, dta: int, perm_a, b: np.ndarray, dtb: int, p
         raise RuntimeError(lib.tvref_last_error().decode())
     n = int(np.prod(shape_c))
     return out.view(np.uint8)[: n * NP[got.value]().itemsize].view(NP[got.value]).reshape(shape_c).copy(), got.value
+
+
+# ---- typecast ---------------------------------------------------------------------------------
+def oracle_cast_valid(sdt: int, ddt: int) -> bool:
+    return bool(oracle().tvo_cast_valid(sdt, ddt))
+
+
+def oracle_typecast(x: np.ndarray, sdt: int, ddt: int) -> np.ndarray:
+    x = np.ascontiguousarray(x)
+    out = np.empty(x.shape, dtype=NP[ddt])
+    rc = oracle().tvo_typecast(C.c_void_p(x.ctypes.data), sdt, C.c_void_p(out.ctypes.data), ddt, C.c_size_t(x.size))
+    if rc != 0:
+        raise RuntimeError(f"Invalid typecast from {DTYPE_NAMES[sdt]} to {DTYPE_NAMES[ddt]}")
+    return out
+
+
+def ref_typecast(x: np.ndarray, sdt: int, ddt: int) -> np.ndarray:
+    """ops::Typecast(const Tensor&, DataType) in the reference (CPU backend)."""
+    lib = ref()
+    x = np.ascontiguousarray(x)
+    out = np.empty(x.shape, dtype=NP[ddt])
+    rc = lib.tvref_typecast(x.ctypes.data, sdt, x.ndim, _i64(x.shape), ddt, out.ctypes.data, out.nbytes)
+    if rc != 0:
+        raise RuntimeError(lib.tvref_last_error().decode())
+    return out

@@ -8,7 +8,7 @@ import pytest
 
 import refcheck as R
 from gpuutil import Dev
-from layout_cases import CONCAT_CASES, LAYOUT_DTYPES, PERMUTE_CASES, SLICE_CASES
+from layout_cases import CONCAT_CASES, LAYOUT_DTYPES, PERMUTE_CASES, SLICE_CASES, pinned_casts, typecast_input
 
 pytestmark = pytest.mark.gpu
 GOLD = np.load(R.GOLDEN_DIR / "golden_layout.npz")
@@ -229,3 +229,60 @@ def test_torch_facing_layout_operators(tv):
         tv.Concat([h, x], 0)
     with pytest.raises(RuntimeError, match="only support 2D"):
         tv.Transpose(h)
+
+
+def gpu_typecast(dev, x, sdt, ddt, misalign=0):
+    p = dev.upload(np.concatenate([np.zeros(misalign, dtype=x.dtype), x]) if misalign else x)
+    out = Out(dev, x.shape, ddt)
+    rc = dev.lib.tvb_typecast(dev.device, p + misalign * x.itemsize, out.ptr, sdt, ddt, x.size, None)
+    dev.check(rc)
+    res = out.read()
+    dev.free(p)
+    return res
+
+
+def test_typecast_matches_the_reference_fixtures_and_the_restatement(dev):
+    """Every cast ops::Typecast allows, bit for bit: against the reference's own outputs where its
+    host arithmetic is sound, against the restatement of the CUDA backend's rounding for all."""
+    for sdt, ddt in pinned_casts():
+        x = typecast_input(sdt)
+        got = gpu_typecast(dev, x, sdt, ddt)
+        assert got.tobytes() == GOLD[f"cast_{sdt}_{ddt}"].tobytes(), (R.DTYPE_NAMES[sdt], R.DTYPE_NAMES[ddt])
+    for sdt in range(8):
+        for ddt in range(8):
+            if not R.oracle_cast_valid(sdt, ddt):
+                continue
+            x = typecast_input(sdt, 1003)
+            assert gpu_typecast(dev, x, sdt, ddt).tobytes() == R.oracle_typecast(x, sdt, ddt).tobytes()
+            # a source that starts off the pack boundary takes the element-wise route
+            assert gpu_typecast(dev, x, sdt, ddt, misalign=1).tobytes() == R.oracle_typecast(x, sdt, ddt).tobytes()
+
+
+def test_typecast_refusals(dev):
+    lib = dev.lib
+    p = dev.alloc(4096)
+    try:
+        for sdt in range(8):
+            for ddt in range(8):
+                rc = lib.tvb_typecast(0, p, p + 2048, sdt, ddt, 16, None)
+                if R.oracle_cast_valid(sdt, ddt):
+                    assert rc == 0
+                else:
+                    assert rc == 3   # TVB_ERR_DTYPE
+                    assert lib.tvb_last_error_string().decode() == \
+                        f"Invalid typecast from {R.DTYPE_NAMES[sdt]} to {R.DTYPE_NAMES[ddt]}"
+        dev.sync()
+        assert lib.tvb_typecast(0, None, p, R.INT8, R.FLOAT32, 16, None) == 1
+    finally:
+        dev.free(p)
+
+
+def test_typecast_then_matmul_equals_the_mixed_pair(dev):
+    """int8 x float16 -> FLOAT32: casting both operands to float32 first (what the promotion means)
+    and multiplying gives the mixed-pair operator's result."""
+    a = R.fill((96, 64), R.INT8, 3, 1); b = R.fill((64, 80), R.FLOAT16, 4)
+    mixed, dt = dev.matmul(a, R.INT8, b, R.FLOAT16)
+    af = gpu_typecast(dev, a, R.INT8, R.FLOAT32); bf = gpu_typecast(dev, b, R.FLOAT16, R.FLOAT32)
+    both, dt2 = dev.matmul(af, R.FLOAT32, bf, R.FLOAT32)
+    assert dt == dt2 == R.FLOAT32
+    assert R.rel_frobenius(mixed, both, R.FLOAT32) <= 1e-5

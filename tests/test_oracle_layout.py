@@ -6,7 +6,7 @@ import pytest
 
 import refcheck as R
 from layout_cases import (CONCAT_CASES, LAYOUT_DTYPES, MUL_VIEW_CASES, PERMUTE_CASES, SLICE_CASES,
-                          pins_view_route)
+                          pinned_casts, pins_view_route, typecast_input)
 
 GOLD = np.load(R.GOLDEN_DIR / "golden_layout.npz")
 F = lambda dt: 0 if dt >= R.BFLOAT16 else 1
@@ -93,3 +93,34 @@ def test_reference_drops_the_offset_of_a_leading_slice_view():
     assert np.array_equal(v, y[0:3]) and not np.array_equal(v, y[2:5])
     st = R.dense_strides(y.shape)
     assert np.array_equal(R.oracle_repack(y, (3, 7), st, 2 * 7), y[2:5])
+
+
+def test_typecast_matches_the_reference_fixtures():
+    """ops::Typecast: every cast the reference allows, bit for bit (float16 -> bfloat16 apart, see
+    oracle/typecast_oracle.c), and the same refusals with the same messages."""
+    casts = pinned_casts()
+    assert len(casts) == 21
+    for sdt, ddt in casts:
+        got = R.oracle_typecast(typecast_input(sdt), sdt, ddt)
+        assert got.tobytes() == GOLD[f"cast_{sdt}_{ddt}"].tobytes(), (R.DTYPE_NAMES[sdt], R.DTYPE_NAMES[ddt])
+    rejected = {str(x).split(":", 1)[0]: str(x).split(":", 1)[1] for x in GOLD["cast_rejected"]}
+    for sdt in range(8):
+        for ddt in range(8):
+            key = f"{sdt}>{ddt}"
+            assert (key in rejected) == (not R.oracle_cast_valid(sdt, ddt)), key
+            if key in rejected:
+                assert rejected[key] == f"Invalid typecast from {R.DTYPE_NAMES[sdt]} to {R.DTYPE_NAMES[ddt]}"
+
+
+def test_typecast_into_half_types_rounds_to_nearest_even():
+    """The casts INTO float16 / bfloat16, checked against numpy (float16) and against the
+    round-to-nearest-even bit arithmetic (bfloat16)."""
+    x = typecast_input(R.FLOAT32)
+    assert R.oracle_typecast(x, R.FLOAT32, R.FLOAT16).tobytes() == x.astype(np.float16).tobytes()
+    h = typecast_input(R.FLOAT16)
+    f = h.astype(np.float32)
+    bits = f.view(np.uint32).astype(np.uint64)
+    want = ((bits + 0x7FFF + ((bits >> 16) & 1)) >> 16).astype(np.uint16)
+    assert R.oracle_typecast(h, R.FLOAT16, R.BFLOAT16).tobytes() == want.tobytes()
+    b = typecast_input(R.BFLOAT16)
+    assert R.oracle_typecast(b, R.BFLOAT16, R.FLOAT16).tobytes() == R.bf16_bits_to_f32(b).astype(np.float16).tobytes()
