@@ -457,11 +457,39 @@ def gpu_arm(args):
                                         "sample": sample + f", 1 run, {t:.2f} s", "host_cpus": os.cpu_count()}
             except Exception as e:  # the baseline must never take the GPU line down
                 line["cpu_baseline"] = {"value": None, "unit": unit, "cores": 0, "kind": "unavailable", "sample": str(e)[:200]}
+        if world == 1 and not args.no_cpu_baseline:
+            line["reference_cuda"] = reference_cuda_sample(cfg_name, unit)
         emit(line)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
     return 0
+
+
+def reference_cuda_sample(cfg_name: str, unit: str):
+    """The reference's own CUDA kernel (mul_cuda_3d, compiled for sm_100 from its sources into
+    oracle/_ref/libtv_ref_cuda.so) on the same configuration and the same GPU, in a process of its
+    own, timed as the reference's tests/mul.cpp times it (wall clock around ops::Mul)."""
+    lib_path = ROOT / "oracle" / "_ref" / "libtv_ref_cuda.so"
+    if not lib_path.exists():
+        return {"value": None, "unit": unit, "kind": "unavailable", "sample": "oracle/_ref/libtv_ref_cuda.so was not built"}
+    cfg, dt, batch, M, K, N, _, _ = CONFIGS[cfg_name]
+    sa = (M, K) if batch is None else (batch, M, K)
+    sb = (K, N) if batch is None else (batch, K, N)
+    reps = 1 if cfg_name in ("c4", "c5") else 3
+    try:
+        proc = subprocess.run([sys.executable, str(ROOT / "oracle" / "refcuda_run.py"), str(dt), str(dt),
+                               str(SEED_BASE + 2 * cfg), str(SEED_BASE + 2 * cfg + 1), ",".join(map(str, sa)),
+                               ",".join(map(str, sb)), str(reps), "-"], capture_output=True, text=True, timeout=600)
+        info = json.loads(proc.stdout.strip().splitlines()[-1])
+        if "error" in info:
+            raise RuntimeError(info["error"])
+        flops = 2.0 * (batch or 1) * M * K * N
+        return {"value": flops / (info["ms_per_call"] * 1e-3) / 1e12, "unit": unit, "ms_per_call": info["ms_per_call"],
+                "reps": reps, "kind": "reference CUDA backend (mul_cuda_3d, 16x16 tiles on CUDA cores) compiled for sm_100",
+                "sample": "the whole configuration, ops::Mul as its tests/mul.cpp times it (result allocation and stream sync inside)"}
+    except Exception as e:
+        return {"value": None, "unit": unit, "kind": "unavailable", "sample": str(e)[:200]}
 
 
 # ---- layout operations (secondary workloads: `--op transpose|permute|slice|concat`) --------------

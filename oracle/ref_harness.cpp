@@ -174,6 +174,28 @@ int tvref_transpose2d(const void* data, int dtype, int64_t rows, int64_t cols, v
   });
 }
 
+// ops::Mul on the device the caller names (0 = Device::CPU, 1 = Device::CUDA: only in the build
+// with the reference's CUDA backend, `make refcuda`), timed the way the reference's own
+// tests/mul.cpp times it: wall clock around ops::Mul, which allocates its result and waits for
+// the stream on every call (src/backend/cuda/mul.cu:64,122).  One untimed call first, then
+// `reps` timed ones; *ms_per_call gets their mean.  The last result is copied to `c`.
+int tvref_mul_on(int device_kind, const void* a, int dtype_a, int rank_a, const int64_t* dims_a, const void* b,
+                 int dtype_b, int rank_b, const int64_t* dims_b, void* c, uint64_t c_bytes, int* dtype_c, int reps,
+                 double* ms_per_call) {
+  return guarded([&] {
+    const via::Device dev = device_kind == 1 ? via::Device::CUDA : via::Device::CPU;
+    Tensor ta(const_cast<void*>(a), shape_of(rank_a, dims_a), static_cast<via::DataType>(dtype_a), dev);
+    Tensor tb(const_cast<void*>(b), shape_of(rank_b, dims_b), static_cast<via::DataType>(dtype_b), dev);
+    Tensor tc = ops::Mul(ta, tb);
+    const double t0 = omp_get_wtime();
+    for (int i = 0; i < reps; ++i) tc = ops::Mul(ta, tb);
+    if (ms_per_call) *ms_per_call = reps > 0 ? (omp_get_wtime() - t0) * 1e3 / reps : 0.0;
+    if (dtype_c) *dtype_c = static_cast<int>(tc.dtype());
+    if (dev != via::Device::CPU) tc.to_host();
+    return emit(tc, c, c_bytes, nullptr);
+  });
+}
+
 // ops::Typecast(const Tensor&, DataType)  (src/ops.cpp:1277-1300)
 int tvref_typecast(const void* data, int dtype, int rank, const int64_t* dims, int dst_dtype, void* out,
                    uint64_t out_bytes) {

@@ -1,0 +1,69 @@
+"""TEST INFRASTRUCTURE — not part of the product.
+
+Runs the REFERENCE's own CUDA backend (oracle/_ref/libtv_ref_cuda.so, built from the reference's
+sources by `make -C oracle refcuda`) on one seeded matmul and reports its time and result:
+
+    python oracle/refcuda_run.py DTYPE_A DTYPE_B SEED_A SEED_B "M,K" "K,N" REPS OUT.npy
+
+It is a program of its own, not a function, because the reference library picks a GPU, makes it
+current and creates a stream from a static initialiser when it is loaded
+(src/init.cpp:18-34, include/backend/cuda/cuda_context.h:14-49): a process that also runs this
+repository's kernels must not load it.  Inputs are generated here from the seeds (the oracle's
+SplitMix64 fill), so nothing large crosses the process boundary; the result is written to
+OUT.npy ("-" = not at all) and one JSON line {"ms_per_call", "dtype_c", "reps"} goes to stdout.
+"""
+import ctypes as C
+import json
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+sys.path.insert(0, str(HERE.parent / "tests"))
+import refcheck as R  # noqa: E402
+
+LIB = HERE / "_ref" / "libtv_ref_cuda.so"
+
+
+def main():
+    dta, dtb, seed_a, seed_b = (int(x) for x in sys.argv[1:5])
+    sa = tuple(int(x) for x in sys.argv[5].split(","))
+    sb = tuple(int(x) for x in sys.argv[6].split(","))
+    reps, out_path = int(sys.argv[7]), sys.argv[8]
+    a = R.fill(sa, dta, seed_a, 0 if dta >= R.BFLOAT16 else 1)
+    b = R.fill(sb, dtb, seed_b, 0 if dtb >= R.BFLOAT16 else 1)
+    # the library prints a device banner from its static initialiser: keep stdout for the JSON line
+    sys.stdout.flush()
+    saved = os.dup(1)
+    os.dup2(2, 1)
+    try:
+        lib = C.CDLL(str(LIB))
+    finally:
+        os.dup2(saved, 1)
+        os.close(saved)
+    i64p = C.POINTER(C.c_int64)
+    lib.tvref_mul_on.argtypes = [C.c_int, C.c_void_p, C.c_int, C.c_int, i64p, C.c_void_p, C.c_int, C.c_int, i64p,
+                                 C.c_void_p, C.c_uint64, C.POINTER(C.c_int), C.c_int, C.POINTER(C.c_double)]
+    lib.tvref_last_error.restype = C.c_char_p
+    lib.tvref_compute_type.argtypes = [C.c_int, C.c_int]
+    dtc = lib.tvref_compute_type(dta, dtb)
+    shape_c = sa[:-1] + (sb[-1],)
+    c = np.empty(shape_c, dtype=R.NP[dtc])
+    got, ms = C.c_int(-1), C.c_double(0.0)
+    i64 = lambda v: (C.c_int64 * len(v))(*v)
+    rc = lib.tvref_mul_on(1, a.ctypes.data, dta, len(sa), i64(sa), b.ctypes.data, dtb, len(sb), i64(sb), c.ctypes.data,
+                          c.nbytes, C.byref(got), reps, C.byref(ms))
+    if rc != 0:
+        print(json.dumps({"error": lib.tvref_last_error().decode()}))
+        return 1
+    assert got.value == dtc
+    if out_path != "-":
+        np.save(out_path, c)
+    print(json.dumps({"ms_per_call": ms.value, "dtype_c": dtc, "reps": reps}))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
