@@ -195,3 +195,34 @@ def test_torch_views_through_ops(tv):
     torch.cuda.synchronize()
     err = (got.double() - want.double()).norm() / want.double().norm()
     assert err.item() <= 1e-5
+
+
+@pytest.mark.parametrize("cfg", [(R.BFLOAT16, 4096, 4096, 4096), (R.INT8, 8192, 8192, 8192), (R.FLOAT32, 2592, 2048, 4096)])
+def test_full_size_transposed_views_equal_the_dense_product(dev, cfg):
+    """At the benchmark sizes, all on the device: B^T and A^T are made with tvb_transpose2d, then
+    A @ (B^T).t(), (A^T).t() @ B and both together must give the dense A @ B — bit for bit for int8
+    (and for the 16-bit types, whose tensor-core sums do not depend on how the operand lies in
+    memory), within 1e-5 for fp32 (its split pass takes another route for a transposed operand)."""
+    dt, M, K, N = cfg
+    lib, es = dev.lib, R.NP[dt]().itemsize
+    dist = 1 if dt == R.INT8 else 0
+    pa, pb = dev.fill((M, K), dt, 7, dist), dev.fill((K, N), dt, 8, dist)
+    pat, pbt = dev.alloc(M * K * es), dev.alloc(K * N * es)
+    pc, pv = dev.alloc(M * N * es), dev.alloc(M * N * es)
+    try:
+        dev.check(lib.tvb_transpose2d(dev.device, pa, pat, dt, M, K, None))   # [K, M]
+        dev.check(lib.tvb_transpose2d(dev.device, pb, pbt, dt, K, N, None))   # [N, K]
+        dev.matmul_ptr(pa, dt, pb, dt, pc, 1, M, K, N)
+        dense = dev.download(pc, (M, N), dt)
+        s3 = lambda *v: (C.c_int64 * 3)(*v)
+        for a_ptr, a_st, b_ptr, b_st in ((pa, s3(0, K, 1), pbt, s3(0, 1, K)), (pat, s3(0, 1, M), pb, s3(0, N, 1)),
+                                         (pat, s3(0, 1, M), pbt, s3(0, 1, K))):
+            dev.check(lib.tvb_matmul_strided(dev.device, a_ptr, b_ptr, pv, dt, dt, dt, 1, M, K, N, a_st, b_st, None, 0))
+            got = dev.download(pv, (M, N), dt)
+            if dt == R.FLOAT32:
+                assert R.rel_frobenius(got, dense, dt) <= 1e-5
+            else:
+                assert got.tobytes() == dense.tobytes()
+    finally:
+        for p in (pa, pb, pat, pbt, pc, pv):
+            dev.free(p)
