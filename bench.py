@@ -356,6 +356,20 @@ def gpu_arm(args):
         dist.barrier()
     check(lib.tvb_sync(local))  # also surfaces a timed-out device wait
     ms_total = ev0.elapsed_time(ev1)
+    # minimum and median of single steps, from a second, untimed pass with an event at every step
+    # boundary (the events themselves cost a few microseconds per step, so the headline figure
+    # above is taken without them)
+    extra = min(args.steps, 50)
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(extra + 1)]
+    marks[0].record()
+    for i in range(extra):
+        step(i)
+        marks[i + 1].record()
+    torch.cuda.synchronize()
+    per_step = sorted(marks[i].elapsed_time(marks[i + 1]) for i in range(extra))
+    ms_min, ms_median = per_step[0], per_step[len(per_step) // 2]
+    if world > 1:
+        dist.barrier()
 
     # ---- end to end through the host-buffer entry point ---------------------------------------
     ha, hb, hc = C.c_void_p(), C.c_void_p(), C.c_void_p()
@@ -425,7 +439,8 @@ def gpu_arm(args):
         unit = "TOP/s" if dt == INT8 else "TFLOP/s"
         line = {
             "metric": "ops::matmul TFLOP/s", "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
-            "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if strong else "weak",
+            "warmup": max(3, args.warmup), "ms_per_step": ms_step, "ms_min": ms_min, "ms_median": ms_median,
+            "higher_is_better": True, "scaling": "strong" if strong else "weak",
             "vs_baseline": None, "dtype": DTYPE_NAME[dt], "data": "synthetic",
             "config": {
                 "workload": WORKLOAD_TEXT[cfg_name], "config": cfg_name, "per_gpu": ("1/%d of the problem per GPU" % world if strong else "one full problem per GPU") if world > 1 else "single GPU",

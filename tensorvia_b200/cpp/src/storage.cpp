@@ -62,24 +62,17 @@ void HostStorage::copy_to(std::shared_ptr<TensorImpl> dst) const {
 std::unique_ptr<TensorImpl> HostStorage::clone() const {
   return std::make_unique<HostStorage>(m_data, m_numel, m_dtype);
 }
-// element idx (row-major over the view's shape) comes from storage[offset + sum coord * stride]
-// (the reference's CPU tensor: include/backend/cpu/cpu_tensor.cpp:32-60)
+// A view of a host tensor is gathered on the GPU like everything else in this library (there is
+// no CPU kernel here): the storage goes to the default device, tvb_repack gathers the view, the
+// dense result comes back.  (The reference's CPU tensor loops on the host,
+// include/backend/cpu/cpu_tensor.cpp:32-60.)
 std::unique_ptr<TensorImpl> HostStorage::clone_as_contiguous(const Metadata& meta) const {
+  auto ctx = cuda_context(default_device());
+  CudaStorage staged(m_data, m_numel, m_dtype, ctx);                 // host -> device
+  std::unique_ptr<TensorImpl> dense = staged.clone_as_contiguous(meta);   // gathered on the device
   auto out = std::make_unique<HostStorage>(nullptr, meta.numel, m_dtype);
-  const size_t es = calc_dtype_size(m_dtype);
-  const char* src = static_cast<const char*>(m_data) + static_cast<size_t>(meta.offset) * es;
-  char* dst = static_cast<char*>(out->data());
-  const size_t nd = meta.shape.size();
-  std::vector<int64_t> coord(nd, 0);
-  for (size_t idx = 0; idx < meta.numel; ++idx) {
-    int64_t off = 0;
-    for (size_t d = 0; d < nd; ++d) off += coord[d] * meta.strides[d];
-    std::memcpy(dst + idx * es, src + off * static_cast<int64_t>(es), es);
-    for (size_t d = nd; d-- > 0;) {
-      if (++coord[d] < meta.shape[d]) break;
-      coord[d] = 0;
-    }
-  }
+  check(tvb_memcpy_d2h(ctx->device(), out->data(), dense->data(), out->bytes(), nullptr), "tvb_memcpy_d2h");
+  ctx->wait();
   return out;
 }
 std::shared_ptr<ContextImpl> HostStorage::context() const {

@@ -211,6 +211,16 @@ int main() {
     Tensor rows = A.slice({{8, 12}}).contiguous();
     EXPECT(rows.at<float>({0, 0}) == A.at<float>({8, 0}) && rows.at<float>({3, 31}) == A.at<float>({11, 31}));
   }
+  // a view of a HOST tensor: gathered through the GPU, result back on the host
+  {
+    std::vector<float> hv = {1, 2, 3, 4, 5, 6};
+    Tensor H(hv.data(), {2, 3}, DataType::FLOAT32, Device::CPU);
+    Tensor Ht = H.t().contiguous();
+    EXPECT(Ht.device() == Device::CPU && Ht.shape() == (std::vector<int64_t>{3, 2}));
+    EXPECT(Ht.at<float>({0, 1}) == 4.f && Ht.at<float>({2, 0}) == 3.f && Ht.at<float>({1, 1}) == 5.f);
+    Tensor P = ops::Mul(H, H.t());        // [2,3] @ [3,2]
+    EXPECT(P.device() == Device::CPU && P.at<float>({0, 0}) == 14.f && P.at<float>({0, 1}) == 32.f && P.at<float>({1, 1}) == 77.f);
+  }
   // ---- Typecast ---------------------------------------------------------------------------------
   {
     std::vector<float> hv = {1.5f, -2.75f, 300.9f, -0.4f, 65504.f, 1e-8f};
