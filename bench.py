@@ -54,7 +54,12 @@ WORKLOAD_TEXT = {
 }
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the
 # ncu captures summarised under profiles/ (absent = no capture of that workload yet)
-NCU_TRAFFIC_BYTES = {"c2": 100.7e6}  # profiles/umma_gemm_pair_bf16_4096x4096x4096.md: 84.6 MB read + 16.1 MB written
+NCU_TRAFFIC_BYTES = {
+    "c2": 100.7e6,   # profiles/umma_gemm_pair_bf16_4096x4096x4096.md: 84.6 MB read + 16.1 MB written
+    "c1": 236.1e6,   # profiles/umma_gemm_pair_counters_c1_c3_c4.md (the GEMM kernel; the split pass moves 164 MB more)
+    "c3": 637.8e6,
+    "c4": 390.9e6,
+}
 L2_BYTES = 126 * 1024 * 1024
 
 

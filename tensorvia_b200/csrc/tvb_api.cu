@@ -526,7 +526,9 @@ int run_umma(Context* c, const UmmaPlan& plan, int dta, int dtb, const Operand& 
   const size_t es = plan.es;
   const uint32_t atom_k = static_cast<uint32_t>(128 / es);  // K elements per 128-byte swizzle atom
   // K elements per pipeline stage, and the K rows of one box of an MN-major operand
-  const uint32_t bk = plan.pair ? atom_k * kPairKAtoms : atom_k;
+  // fp32 on CTA pairs: all three products of a K atom from one stage (A_hi, A_lo, B_hi, B_lo)
+  const bool fused3 = plan.op == OP_TF32 && plan.pair && plan.passes == 3 && getenv("TVB_NO_FUSED3") == nullptr;
+  const uint32_t bk = plan.pair && !fused3 ? atom_k * kPairKAtoms : atom_k;
   const uint32_t chunk_n = static_cast<uint32_t>(128 / es);
   auto misaligned = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) != 0; };
   auto round_up = [](size_t v, size_t m) { return (v + m - 1) / m * m; };
@@ -571,7 +573,8 @@ int run_umma(Context* c, const UmmaPlan& plan, int dta, int dtb, const Operand& 
     const uint32_t shift = kb / 16;
     const uint32_t kw = kb / 2 > shift ? kb / 2 - shift : 0;
     // stages x passes = MMA batches per tile: fp32 runs three per stage
-    const uint32_t work = kb * static_cast<uint32_t>(plan.passes);
+    // (a fused fp32 stage carries 12 MMAs, one and a half of the others' 8)
+    const uint32_t work = fused3 ? kb * 3 / 2 : kb * static_cast<uint32_t>(plan.passes);
     if (rest > 0 && 2 * rest <= pairs && work >= 32 && kw >= 1 &&
         static_cast<size_t>(rest) * 16 <= static_cast<size_t>(Context::kMaxFlags) &&
         getenv("TVB_NO_SPLIT_K") == nullptr) {
@@ -706,7 +709,8 @@ int run_umma(Context* c, const UmmaPlan& plan, int dta, int dtb, const Operand& 
   p.m_tiles = static_cast<int32_t>((M + plan.tile_m - 1) / plan.tile_m);
   p.n_tiles = static_cast<int32_t>((N + plan.block_n - 1) / plan.block_n);
   p.k_blocks = static_cast<int32_t>((K + bk - 1) / bk);
-  p.passes = plan.passes;
+  p.passes = fused3 ? 1 : plan.passes;
+  p.fused3 = fused3 ? 1 : 0;
   // fp32: 256 elements of K per TMEM-resident partial sum (TVB_K_CHUNK, in stages, overrides)
   p.k_chunk_blocks = static_cast<int32_t>(256 / bk);
   if (const char* e = getenv("TVB_K_CHUNK")) {

@@ -81,6 +81,8 @@ struct UmmaGemmParams {
   int32_t M, N, K, batch;
   int32_t m_tiles, n_tiles, k_blocks;
   int32_t passes;        // 1, or 3 when fp32 runs as (A_lo,B_hi), (A_hi,B_lo), (A_hi,B_hi)
+  int32_t fused3;        // CTA-pair kernel, fp32: a stage holds A_hi, A_lo, B_hi, B_lo of one 128-byte K atom and
+                         // feeds all three products from it (then `passes` is 1 and k_blocks counts atoms)
   int32_t k_chunk_blocks;// stages of K summed inside TMEM before the sum moves to registers
   uint32_t total_tiles;  // batch * m_tiles * n_tiles
   // CTA-pair kernel only.  Work items [0, split_from) are whole tiles.  The tiles of an

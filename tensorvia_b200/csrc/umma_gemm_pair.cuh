@@ -152,7 +152,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_con
   if (warp == 0 && lane == 0) {
     ptx::prefetch_tmap(&tmA0);
     ptx::prefetch_tmap(&tmB0);
-    if (p.passes > 1) {
+    if (p.passes > 1 || p.fused3) {
       ptx::prefetch_tmap(&tmA1);
       ptx::prefetch_tmap(&tmB1);
     }
@@ -167,6 +167,12 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_con
   ptx::tc_fence_after();
   const uint32_t tmem_base = *slot_ptr;
 
+  // fp32 with all three products per stage: the stage's A half holds [A_hi atom | A_lo atom], its
+  // B half [B_hi atom | B_lo atom]; every operand byte is then fetched once per K atom instead
+  // of hi twice and lo once (a third less traffic into shared memory, which the MMAs' own
+  // operand reads already load to half of its bandwidth)
+  const bool fused3 = OP == OP_TF32 && KATOMS == 2 && p.fused3 != 0;
+  const int bk_elems = fused3 ? ATOM_K : BK;     // K elements a stage covers
   const int kc = CHUNKED ? p.k_chunk_blocks : p.k_blocks;
   const int chunks = (p.k_blocks + kc - 1) / kc;
 
@@ -191,6 +197,12 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_con
             const CUtensorMap* ma = (p.passes > 1 && pass == 0) ? &tmA1 : &tmA0;
             const CUtensorMap* mb = (p.passes > 1 && pass == 1) ? &tmB1 : &tmB0;
             if (leader) ptx::mbar_expect_tx(full_bar(stage), 2 * Cfg::STAGE_BYTES);
+            if (fused3) {
+              ptx::tma_load_3d_pair(a_smem(stage), &tmA0, full_bar_leader(stage), kb * bk_elems, row0, b);
+              ptx::tma_load_3d_pair(a_smem(stage) + ATOM_BYTES, &tmA1, full_bar_leader(stage), kb * bk_elems, row0, b);
+              ptx::tma_load_3d_pair(b_smem(stage), &tmB0, full_bar_leader(stage), kb * bk_elems, col0, b);
+              ptx::tma_load_3d_pair(b_smem(stage) + ATOM_BYTES, &tmB1, full_bar_leader(stage), kb * bk_elems, col0, b);
+            } else {
             if constexpr (A_MN) {
               // A stored [K, M]: boxes of 128 B of M x BK rows of K, like MN-major B
 #pragma unroll
@@ -213,6 +225,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_con
               for (int j = 0; j < KATOMS; ++j)
                 ptx::tma_load_3d_pair(b_smem(stage) + j * ATOM_BYTES, mb, full_bar_leader(stage),
                                       kb * BK + j * ATOM_K, col0, b);
+            }
             }
             if (++stage == STAGES) {
               stage = 0;
@@ -255,6 +268,19 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_con
             ptx::tc_fence_after();
             const uint32_t a0 = a_smem(stage);
             const uint32_t b0 = b_smem(stage);
+            if (fused3) {
+              // per 32-byte K step: A_lo*B_hi, A_hi*B_lo, A_hi*B_hi (small terms first)
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const uint64_t ahi = ptx::make_smem_desc(a0 + k * 32, 16, 1024);
+                const uint64_t alo = ptx::make_smem_desc(a0 + ATOM_BYTES + k * 32, 16, 1024);
+                const uint64_t bhi = ptx::make_smem_desc(b0 + k * 32, 16, 1024);
+                const uint64_t blo = ptx::make_smem_desc(b0 + ATOM_BYTES + k * 32, 16, 1024);
+                ptx::tc_mma_pair<T::MMA>(d_tmem, alo, bhi, IDESC, (it > 0 || k > 0) ? 1u : 0u);
+                ptx::tc_mma_pair<T::MMA>(d_tmem, ahi, blo, IDESC, 1u);
+                ptx::tc_mma_pair<T::MMA>(d_tmem, ahi, bhi, IDESC, 1u);
+              }
+            } else {
 #pragma unroll
             for (int k = 0; k < KSTEPS; ++k) {
               const uint32_t koff = (k >> 2) * ATOM_BYTES + (k & 3) * 32;  // atom, then 32 B steps inside it
@@ -263,6 +289,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_con
               const uint64_t bdesc = B_MN ? ptx::make_smem_desc(b0 + k * B_KSTEP_BYTES, CHUNK_BYTES, 1024)
                                           : ptx::make_smem_desc(b0 + koff, 16, 1024);
               ptx::tc_mma_pair<T::MMA>(d_tmem, adesc, bdesc, IDESC, (it > 0 || k > 0) ? 1u : 0u);
+            }
             }
             ptx::tc_commit_pair(empty_bar(stage), 3);  // stage free in both CTAs
             if (++stage == STAGES) {
