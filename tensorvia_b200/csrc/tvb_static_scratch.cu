@@ -210,6 +210,7 @@ extern "C" int tvb_matmul_f32_static(int device, const void* A, const void* B, v
   p.passes = 3;
   p.c_vec = 1;
   p.fused3 = 0;
+  p.group = 16;
   p.k_chunk_blocks = 8;
   const int64_t tiles = batch * p.m_tiles * p.n_tiles;
   if (tiles > 0x7FFFFFFFll) return fail(TVB_ERR_SHAPE, "too many output tiles");

@@ -85,6 +85,7 @@ struct UmmaGemmParams {
                          // feeds all three products from it (then `passes` is 1 and k_blocks counts atoms)
   int32_t k_chunk_blocks;// stages of K summed inside TMEM before the sum moves to registers
   uint32_t total_tiles;  // batch * m_tiles * n_tiles
+  uint32_t group;        // tile-rows per group of the tile walk (see decode_tile)
   // CTA-pair kernel only.  Work items [0, split_from) are whole tiles.  The tiles of an
   // incomplete last wave, [split_from, total_tiles), are each shared by `split_parts` pairs
   // that take consecutive ranges of K: item split_from + j is part j % split_parts of tile
@@ -143,12 +144,13 @@ struct UmmaGemmConfig {
 
 __device__ __forceinline__ void decode_tile(uint32_t tile, const UmmaGemmParams& p, int& b, int& mt,
                                             int& nt) {
-  // Groups of 8 tile-rows are walked column by column, so the CTAs that run at the
-  // same time share a short band of A and a short band of B in L2.
+  // Groups of `p.group` tile-rows are walked column by column, so the CTAs that run at the
+  // same time share a band of A (the group's rows, which stay in L2 for the whole group) and a
+  // short band of B (streamed once per group).
   const uint32_t per_batch = static_cast<uint32_t>(p.m_tiles) * static_cast<uint32_t>(p.n_tiles);
   const uint32_t bb = tile / per_batch;
   const uint32_t r = tile - bb * per_batch;
-  constexpr uint32_t GROUP = 8;
+  const uint32_t GROUP = p.group;
   const uint32_t group_sz = GROUP * static_cast<uint32_t>(p.n_tiles);
   const uint32_t g = r / group_sz;
   const uint32_t first_m = g * GROUP;
