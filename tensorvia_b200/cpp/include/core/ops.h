@@ -20,6 +20,14 @@ Tensor Mul(const Tensor& a, const Tensor& b);
 // the name the reference's README uses for the same function
 inline Tensor matmul(const Tensor& a, const Tensor& b) { return Mul(a, b); }
 
+// The same product with the rows of A (2-D) or the batches (3-D) split over the first `n_gpus`
+// devices of the box, one host thread per device: device r gets its slab of A (cut on 128-row
+// tile boundaries), a copy of B (2-D) or its batches of B (3-D), multiplies, and its slab of C
+// lands in the result.  K is never split, so every row equals the single-device row bit for
+// bit.  Operands may live on the host or on a device; the result is a host tensor.  (New: the
+// reference is single-device; its Tensor::to_device(id) ignores the id, src/tensor.cpp:486-509.)
+Tensor matmul_sharded(const Tensor& a, const Tensor& b, int n_gpus);
+
 // ---- layout operations either side of the matmul (the scatter and gather steps of a sharded
 // product are exactly these) -------------------------------------------------------------------
 // A dense copy of the window [first, second) of every dimension; one range per dimension.

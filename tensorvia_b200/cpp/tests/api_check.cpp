@@ -2,12 +2,14 @@
 // rules and messages of ops::Mul, the result dtypes, values against a plain host loop, value
 // semantics of Tensor, and host<->device moves.  Exit code 0 = all passed.
 #include <cmath>
+#include <cstring>
 #include <cstdio>
 #include <functional>
 #include <string>
 #include <vector>
 
 #include "ops.h"
+#include "tvb.h"
 using namespace via;
 
 static int g_failed = 0;
@@ -220,6 +222,28 @@ int main() {
     EXPECT(Ht.at<float>({0, 1}) == 4.f && Ht.at<float>({2, 0}) == 3.f && Ht.at<float>({1, 1}) == 5.f);
     Tensor P = ops::Mul(H, H.t());        // [2,3] @ [3,2]
     EXPECT(P.device() == Device::CPU && P.at<float>({0, 0}) == 14.f && P.at<float>({0, 1}) == 32.f && P.at<float>({1, 1}) == 77.f);
+  }
+  // ---- matmul_sharded: rows / batches over every GPU of the box, one thread each -----------------
+  {
+    int gpus = 0;
+    EXPECT(tvb_device_count(&gpus) == 0 && gpus >= 1);
+    const int M = 700, K = 96, N = 200;
+    std::vector<int8_t> ha(M * K), hb(K * N);
+    for (size_t i = 0; i < ha.size(); ++i) ha[i] = static_cast<int8_t>((i * 31) % 21 - 10);
+    for (size_t i = 0; i < hb.size(); ++i) hb[i] = static_cast<int8_t>((i * 17) % 21 - 10);
+    Tensor A(ha.data(), {M, K}, DataType::INT8, Device::CPU), B(hb.data(), {K, N}, DataType::INT8, Device::CPU);
+    Tensor whole = ops::Mul(A, B);
+    for (int n = 1; n <= gpus && n <= 4; ++n) {
+      Tensor sharded = ops::matmul_sharded(A, B, n);
+      EXPECT(sharded.device() == Device::CPU && sharded.shape() == whole.shape() && sharded.dtype() == DataType::INT8);
+      EXPECT(std::memcmp(sharded.data(), whole.data(), static_cast<size_t>(M) * N) == 0);
+    }
+    std::vector<float> h3a(5 * 40 * 24, 0.5f), h3b(5 * 24 * 16, 0.25f);
+    Tensor A3(h3a.data(), {5, 40, 24}, DataType::FLOAT32, Device::CUDA), B3(h3b.data(), {5, 24, 16}, DataType::FLOAT32, Device::CUDA);
+    Tensor s3 = ops::matmul_sharded(A3, B3, gpus > 4 ? 4 : gpus);
+    EXPECT(s3.shape() == (std::vector<int64_t>{5, 40, 16}) && s3.at<float>({4, 39, 15}) == 3.0f && s3.at<float>({0, 0, 0}) == 3.0f);
+    EXPECT(thrown([&] { ops::matmul_sharded(A, B, gpus + 1); }).find("GPUs asked") != std::string::npos);
+    EXPECT(thrown([&] { ops::matmul_sharded(A, A, 1); }) == "Tensors common dim must match,but 700 and 700");
   }
   // ---- Typecast ---------------------------------------------------------------------------------
   {
