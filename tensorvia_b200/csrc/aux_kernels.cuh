@@ -140,6 +140,59 @@ split_tf32_transpose_kernel(const T* __restrict__ src, float* __restrict__ hi,
   }
 }
 
+// The transposing split at full width for fp32 sources whose rows and columns are whole 16-byte
+// vectors (N and K multiples of 4, sk and sb multiples of 4, 16-byte aligned bases, kp == K):
+// 16-byte loads along n, 16-byte stores along k.  A tile is 32 values of n by 128 of k; every
+// thread loads four float4 (rows k, k+32, k+64, k+96 of its n vector), splits them, and writes
+// single words into two shared tiles whose rows run along k; the tiles are not padded: their
+// 16-byte groups are XOR-swizzled with the thread's n-vector index, which keeps the word stores
+// of a warp on 32 different banks and the 16-byte reads of the second phase conflict-free.
+// grid = (ceil(N/32), ceil(K/128), batch).
+static __global__ void __launch_bounds__(256)
+split_tf32_transpose_vec_kernel(const float* __restrict__ src, float* __restrict__ hi, float* __restrict__ lo,
+                                int K, int N, int64_t sb, int64_t sk) {
+  __shared__ uint4 th[32][32];
+  __shared__ uint4 tl[32][32];
+  const float* sbase = src + static_cast<int64_t>(blockIdx.z) * sb;
+  const size_t ooff = static_cast<size_t>(blockIdx.z) * N * K;
+  const int n0 = blockIdx.x * 32, k0 = blockIdx.y * 128;
+  const int uv = threadIdx.x & 7;
+  const int n = n0 + uv * 4;
+  float4 v[4];
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int k = k0 + (threadIdx.x >> 3) + 32 * r;
+    v[r] = (n < N && k < K) ? *reinterpret_cast<const float4*>(sbase + static_cast<int64_t>(k) * sk + n)
+                            : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  float* fh = reinterpret_cast<float*>(th);
+  float* fl = reinterpret_cast<float*>(tl);
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int lg = (threadIdx.x >> 3) + 32 * r;    // k within the tile
+    const int col = lg ^ (uv << 2);
+    const float x[4] = {v[r].x, v[r].y, v[r].z, v[r].w};
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+      const float h = round_tf32(x[m]);
+      fh[(uv * 4 + m) * 128 + col] = h;
+      fl[(uv * 4 + m) * 128 + col] = round_tf32(x[m] - h);
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int it = threadIdx.x; it < 32 * 32; it += 256) {
+    const int c = it & 31, row = it >> 5;          // row: n within the tile, c: 16-byte group along k
+    const int nn = n0 + row, k = k0 + c * 4;
+    if (nn < N && k < K) {
+      const int sw = c ^ ((row >> 2) & 7);
+      const size_t o = ooff + static_cast<size_t>(nn) * K + k;
+      *reinterpret_cast<uint4*>(hi + o) = th[row][sw];
+      *reinterpret_cast<uint4*>(lo + o) = tl[row][sw];
+    }
+  }
+}
+
 // ---- ops::Typecast ---------------------------------------------------------------------------
 // One element converted as the reference's cast_cuda does (src/backend/cuda/typecast.cu:6-27):
 // static_cast between the C types; float -> half / bfloat16 round to nearest even; half <->

@@ -484,8 +484,25 @@ cudaError_t launch_split_transpose_t(const void* src, float* hi, float* lo, int6
                                      int64_t sb, int64_t sk, cudaStream_t s) {
   // src(z, k, n) = src[z*sb + k*sk + n] -> hi/lo [batch][N][kp]; gridDim.z carries at most 65535
   // batches per launch
+  // fp32 in whole, aligned 16-byte vectors on both sides: the 16-byte kernel
+  const bool vec = std::is_same_v<T, float> && N % 4 == 0 && K % 4 == 0 && kp == K && sk % 4 == 0 &&
+                   (batch == 1 || sb % 4 == 0) && reinterpret_cast<uintptr_t>(src) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(hi) % 16 == 0 && reinterpret_cast<uintptr_t>(lo) % 16 == 0 &&
+                   (K + 127) / 128 <= 65535 && getenv("TVB_NO_VEC_SPLIT") == nullptr;
   for (int64_t b0 = 0; b0 < batch; b0 += 65535) {
     const int nbz = static_cast<int>(batch - b0 < 65535 ? batch - b0 : 65535);
+    if constexpr (std::is_same_v<T, float>) {
+      if (vec) {
+        dim3 vgrid(static_cast<unsigned>((N + 31) / 32), static_cast<unsigned>((K + 127) / 128), nbz);
+        split_tf32_transpose_vec_kernel<<<vgrid, 256, 0, s>>>(static_cast<const float*>(src) + b0 * sb,
+                                                              hi + static_cast<size_t>(b0) * N * kp,
+                                                              lo + static_cast<size_t>(b0) * N * kp, K, N, sb, sk);
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+        continue;
+      }
+    }
     dim3 grid(static_cast<unsigned>((N + 31) / 32), static_cast<unsigned>((K + 31) / 32), nbz);
     split_tf32_transpose_kernel<T><<<grid, 256, 0, s>>>(
         static_cast<const T*>(src) + b0 * sb, hi + static_cast<size_t>(b0) * N * kp,
