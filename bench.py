@@ -322,9 +322,33 @@ def gpu_arm(args):
         c_local = torch.empty((M, N), dtype=tdt, device="cuda")
         gather_bufs = [torch.empty((n_, N), dtype=tdt, device="cuda") for n_ in counts] if rank == 0 else None
 
+    # ---- optional: the operands as transposed views (2-D problems, one GPU) ------------------------
+    # B^T ([N,K]) and / or A^T ([K,M]) are made once with tvb_transpose2d; the timed call is then
+    # tvb_matmul_strided on the .t() views of those arrays, which are read in place.
+    view = args.view if (world == 1 and batch is None) else "none"
+    view_sets = []
+    if view != "none":
+        i64x3 = lambda *v: (C.c_int64 * 3)(*v)
+        for (pa, pb, pc) in sets:
+            va, vb = pa, pb
+            sa_, sb_ = i64x3(0, K, 1), i64x3(0, N, 1)
+            if view in ("at", "both"):
+                va = dalloc(bytes_a)
+                check(lib.tvb_transpose2d(local, pa, va, dt, M, K, sp))
+                sa_ = i64x3(0, 1, M)
+            if view in ("bt", "both"):
+                vb = dalloc(bytes_b)
+                check(lib.tvb_transpose2d(local, pb, vb, dt, K, N, sp))
+                sb_ = i64x3(0, 1, K)
+            view_sets.append((va, sa_, vb, sb_))
+        torch.cuda.synchronize()
+
     def step(i):
         pa, pb, pc = sets[i % nsets]
-        if gather == "fused":
+        if view != "none":
+            va, sa_, vb, sb_ = view_sets[i % nsets]
+            check(lib.tvb_matmul_strided(local, va, vb, pc, dt, dt, dtc, 1, M, K, N, sa_, sb_, sp, 0))
+        elif gather == "fused":
             check(lib.tvb_matmul(local, pa, pb, shared_base + begin * N * es, dt, dt, dtc, nb, M, K, N, sp))
         elif gather == "nccl":
             check(lib.tvb_matmul(local, pa, pb, c_local.data_ptr(), dt, dt, dtc, nb, M, K, N, sp))
@@ -453,6 +477,9 @@ def gpu_arm(args):
                 "kernel": f"tcgen05 {info.tile_m}x{info.tile_n}x{info.tile_k}, {info.stages} stages, {info.ctas} CTAs, {info.passes} pass(es)" if info.algo == 1 else "simt",
                 "l2": f"{nsets} rotating operand sets ({nsets * per_set >> 20} MiB) exceed the {L2_BYTES >> 20} MiB L2",
                 "inputs": "SplitMix64 counter-based, seeds 0x5EED0000+2*cfg (A), +1 (B)",
+                "view": {"none": "dense row-major operands", "bt": "B is the .t() view of a dense [N,K] array, read in place",
+                         "at": "A is the .t() view of a dense [K,M] array, read in place",
+                         "both": "A and B are .t() views of dense [K,M] and [N,K] arrays, read in place"}[view],
                 "gather": {"none": "none: C stays sharded", "nccl": "C slabs sent to rank 0 over NCCL after each product, inside the timed region",
                            "fused": "every rank's GEMM epilogue stores its C tiles into rank 0's buffer over NVLink (peer stores), inside the timed region"}[gather],
             },
@@ -722,6 +749,8 @@ def main():
     ap.add_argument("--rows", type=int, default=16384, help="layout operations: rows of the source")
     ap.add_argument("--cols", type=int, default=16384, help="layout operations: columns of the source")
     ap.add_argument("--elem-bytes", type=int, default=2, choices=[1, 2, 4, 8], help="layout operations: element size")
+    ap.add_argument("--view", default="none", choices=["none", "bt", "at", "both"],
+                    help="one GPU, 2-D problems: give B and / or A as transposed views (tvb_matmul_strided)")
     ap.add_argument("--gather", default="none", choices=["none", "nccl", "fused"],
                     help="with --scaling strong on a 2-D problem: also bring the whole C to rank 0 in every step")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
