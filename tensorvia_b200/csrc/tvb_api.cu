@@ -570,7 +570,7 @@ int run_umma(Context* c, const UmmaPlan& plan, int dta, int dtb, const Operand& 
   Staged sa{opa.ptr, opa.ptr, false, 0, 0}, sb{opb.ptr, opb.ptr, false, 0, 0};
 
   // Shared-tile plan of the pair kernel (decided here because its scratch shares the block)
-  uint32_t sk_rest = 0, sk_kw = 0;
+  uint32_t sk_rest = 0, sk_kw = 0, sk_parts = 1;
   uint32_t pairs = 0;
   const int32_t k_blocks = static_cast<int32_t>((K + bk - 1) / bk);
   const uint32_t total_tiles = static_cast<uint32_t>(batch * ((M + plan.tile_m - 1) / plan.tile_m) *
@@ -587,19 +587,37 @@ int run_umma(Context* c, const UmmaPlan& plan, int dta, int dtb, const Operand& 
     // on (fp32: 32 stage-passes).
     const uint32_t rest = total_tiles % pairs;
     const uint32_t kb = static_cast<uint32_t>(k_blocks);
-    const uint32_t shift = kb / 16;
-    const uint32_t kw = kb / 2 > shift ? kb / 2 - shift : 0;
     // stages x passes = MMA batches per tile: fp32 runs three per stage
     // (a fused fp32 stage carries 12 MMAs, one and a half of the others' 8)
     const uint32_t work = fused3 ? kb * 3 / 2 : kb * static_cast<uint32_t>(plan.passes);
-    if (rest > 0 && 2 * rest <= pairs && work >= 32 && kw >= 1 &&
-        static_cast<size_t>(rest) * 16 <= static_cast<size_t>(Context::kMaxFlags) &&
+    // When the last wave is a quarter full or less (a problem of few tiles and a long K above
+    // all: 1024 x 1024 x 16384 has 16 tiles for 74 pairs), its tiles are shared by up to eight
+    // pairs, as long as every share keeps 16 stages' worth of MMAs.
+    uint32_t parts = rest > 0 ? std::min<uint32_t>(8, pairs / rest) : 1;
+    while (parts > 2 && work / parts < 16) --parts;
+    if (const char* e = getenv("TVB_SPLIT_PARTS")) parts = std::min<uint32_t>(parts, static_cast<uint32_t>(std::max(1, atoi(e))));
+    // every share but the owner's takes a little less than kb / parts stages, so that its sums
+    // are in memory when the owner's own sum is complete
+    uint32_t kw;
+    if (parts <= 2) {
+      const uint32_t shift = kb / 16;
+      kw = kb / 2 > shift ? kb / 2 - shift : 0;
+    } else {
+      // the owner keeps `extra` stages more than an even share: about the time the others need
+      // to get their sums out (a stage of eight MMAs lasts ~0.65 us, a hand-over ~4 us)
+      const uint32_t even = kb / parts;
+      const uint32_t extra = std::min<uint32_t>(even / 2, std::max<uint32_t>(6, kb / (8 * parts)));
+      kw = (kb - extra) / parts;
+    }
+    if (parts >= 2 && work >= 32 && kw >= 1 &&
+        static_cast<size_t>(rest) * (parts - 1) * 16 <= static_cast<size_t>(Context::kMaxFlags) &&
         getenv("TVB_NO_SPLIT_K") == nullptr) {
       sk_rest = rest;
       sk_kw = kw;
+      sk_parts = parts;
     }
   }
-  const size_t partial_bytes = static_cast<size_t>(sk_rest) * 2 * 128 * 256 * sizeof(uint32_t);
+  const size_t partial_bytes = static_cast<size_t>(sk_rest) * (sk_parts - 1) * 2 * 128 * 256 * sizeof(uint32_t);
 
   std::unique_lock<std::mutex> lock(c->mu, std::defer_lock);
   if (plan.op == OP_TF32) {
@@ -760,9 +778,9 @@ int run_umma(Context* c, const UmmaPlan& plan, int dta, int dtb, const Operand& 
   if (plan.pair) {
     if (sk_rest > 0) {
       p.split_from = p.total_tiles - sk_rest;
-      p.split_parts = 2;
+      p.split_parts = sk_parts;
       p.split_kw = sk_kw;
-      p.total_items = p.split_from + sk_rest * 2;
+      p.total_items = p.split_from + sk_rest * sk_parts;
       p.partial = static_cast<uint32_t*>(c->ws);   // the front of the scratch block
       if (++c->sk_epoch == 0) ++c->sk_epoch;
       p.epoch = c->sk_epoch;

@@ -472,11 +472,13 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_con
         if (w.parts > 1) {
           bool there = true;
           if (lane == 0) {
-            const volatile uint32_t* f = reinterpret_cast<const volatile uint32_t*>(flag_of(w.slot));
-            const uint64_t t0 = ptx::globaltimer_ns();
-            while (*f != p.epoch) {
-              if (ptx::globaltimer_ns() - t0 > p.wait_limit_ns) { there = false; break; }
-              __nanosleep(200);
+            for (uint32_t q = 0; q + 1 < w.parts && there; ++q) {
+              const volatile uint32_t* f = reinterpret_cast<const volatile uint32_t*>(flag_of(w.slot + q));
+              const uint64_t t0 = ptx::globaltimer_ns();
+              while (*f != p.epoch) {
+                if (ptx::globaltimer_ns() - t0 > p.wait_limit_ns) { there = false; break; }
+                __nanosleep(200);
+              }
             }
             __threadfence();
           }
@@ -486,10 +488,12 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_con
             ok = false;
             break;
           }
+          for (uint32_t q = 0; q + 1 < w.parts; ++q) {
 #pragma unroll
-          for (int g = 0; g < HALF_N / 4; ++g) {
-            const float4 u = __ldcg(partial_vec(w.slot, g));
-            acc[4 * g] += u.x; acc[4 * g + 1] += u.y; acc[4 * g + 2] += u.z; acc[4 * g + 3] += u.w;
+            for (int g = 0; g < HALF_N / 4; ++g) {
+              const float4 u = __ldcg(partial_vec(w.slot + q, g));
+              acc[4 * g] += u.x; acc[4 * g + 1] += u.y; acc[4 * g + 2] += u.z; acc[4 * g + 3] += u.w;
+            }
           }
         }
         const int row = mt * Cfg::BLOCK_M + static_cast<int>(rank) * 128 + quad * 32 + lane;

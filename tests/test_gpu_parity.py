@@ -287,3 +287,25 @@ def test_whole_row_stores_of_the_peer_memory_epilogue(dev, dt, monkeypatch):
     monkeypatch.setenv("TVB_FORCE_ROW_STORES", "1")
     got, _ = dev.matmul(A, dt, B, dt)
     assert got.tobytes() == want.tobytes()
+
+
+@pytest.mark.parametrize("case", [(R.BFLOAT16, 1024, 8192, 1024), (R.INT8, 512, 16384, 768), (R.FLOAT32, 1024, 4096, 512),
+                                  (R.FLOAT16, 300, 6144, 700)])
+def test_few_tiles_long_k_shared_by_up_to_four_pairs(dev, case, monkeypatch):
+    """A problem with fewer tiles than a quarter of the CTA pairs and a long K: every tile's K range
+    is shared by up to four pairs.  Same results as with the sharing switched off (int8 bit for bit,
+    floats to rounding), and as the restatement."""
+    dt, M, K, N = case
+    A = R.fill((M, K), dt, 51, F(dt)); B = R.fill((K, N), dt, 52, F(dt))
+    monkeypatch.delenv("TVB_NO_SPLIT_K", raising=False)
+    got, dtc = dev.matmul(A, dt, B, dt)
+    monkeypatch.setenv("TVB_NO_SPLIT_K", "1")
+    whole, _ = dev.matmul(A, dt, B, dt)
+    monkeypatch.delenv("TVB_NO_SPLIT_K", raising=False)
+    if dt == R.INT8:
+        assert got.tobytes() == whole.tobytes()
+    else:
+        assert R.rel_frobenius(got, whole, dtc) <= (1e-5 if dt == R.FLOAT32 else 1e-2)
+    if M * N * K <= 1024 * 4096 * 512:
+        exp, dte = R.oracle_matmul(A, dt, B, dt, "cuda")
+        assert_matches(got, dtc, exp, dte, what=f"shared tiles {case}")
