@@ -243,7 +243,7 @@ struct UmmaPlan {
 
 // Problems the tensor-core kernels take: same-dtype f16 / bf16 / int8 / fp32 of any shape.
 bool umma_eligible(int dta, int dtb, int64_t batch, int64_t M, int64_t K, int64_t N, const void* A,
-                   const void* B, const void* C, UmmaPlan* plan) {
+                   const void* B, const void* C, UmmaPlan* plan, int sm_count) {
   UmmaPlan p;
   if (dta != dtb) {
     // mixed pairs whose result is FLOAT32 (int8 x f16, bf16 x f16, int32 x fp32, ...): both
@@ -278,7 +278,13 @@ bool umma_eligible(int dta, int dtb, int64_t batch, int64_t M, int64_t K, int64_
   // outweighs leaving some pairs idle on small problems (measured from 256x256 outputs up:
   // 2048^3 19.6 vs 20.6 us, 1024x4096x1024 23.0 vs 29.4 us).  TVB_CTA_PAIR overrides.
   {
-    p.pair = p.block_n == 256 && M > 128;
+    // A single 128-row tile per column also goes to pairs when its tiles fit one wave of pairs:
+    // half of each pair's rows are padding then, but the MMAs still run at 128 cycles and the
+    // tiles can be shared along K, which one CTA per tile cannot do (measured, bf16:
+    // 128x16384x512 94.9 -> 36.9 us, 128x8192x8192 56.0 -> 39.8 us; with more tiles than pairs,
+    // 100x1024x30000, one CTA per tile stays ahead: 17.5 against 20.1 us).
+    const int64_t wide_tiles = batch * ((N + 255) / 256);
+    p.pair = p.block_n == 256 && (M > 128 || wide_tiles <= sm_count / 2);
     if (const char* e = getenv("TVB_CTA_PAIR")) p.pair = p.block_n == 256 && atoi(e) != 0;
     if (p.pair) {
       p.tile_m = 256;
@@ -843,7 +849,7 @@ int matmul_views(int device, const Operand& a, const Operand& b, void* C, int dt
   cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : c->stream;
 
   UmmaPlan plan;
-  const bool can_umma = umma_eligible(dta, dtb, batch, M, K, N, A, B, C, &plan);
+  const bool can_umma = umma_eligible(dta, dtb, batch, M, K, N, A, B, C, &plan, c->sm_count);
   if (algo == TVB_ALGO_TCGEN05 && !can_umma)
     return fail(TVB_ERR_UNSUPPORTED,
                 "the tcgen05 path takes f16 x f16, bf16 x bf16, int8 x int8, fp32 x fp32 and the mixed pairs "
@@ -1484,7 +1490,7 @@ int tvb_matmul_plan(int device, int dta, int dtb, int64_t batch, int64_t M, int6
   if (rc != TVB_OK) return rc;
   memset(out, 0, sizeof *out);
   UmmaPlan plan;
-  const bool can = umma_eligible(dta, dtb, batch, M, K, N, nullptr, nullptr, nullptr, &plan);
+  const bool can = umma_eligible(dta, dtb, batch, M, K, N, nullptr, nullptr, nullptr, &plan, c->sm_count);
   if (algo == TVB_ALGO_TCGEN05 && !can) return fail(TVB_ERR_UNSUPPORTED, "problem is not eligible for the tcgen05 path");
   if (can && algo != TVB_ALGO_SIMT) {
     out->algo = TVB_ALGO_TCGEN05;

@@ -150,9 +150,13 @@ def test_kernel_choice(dev, tv):
     # large problems run on CTA pairs (256 x 256 tiles, 128 elements of K per stage) ...
     info = tv.ops.plan(R.BFLOAT16, R.BFLOAT16, 1, 4096, 4096, 4096)
     assert (info.algo, info.tile_m, info.tile_n, info.tile_k, info.passes) == (TCGEN05, 256, 256, 128, 1)
-    # ... problems of at most 128 rows or 128 columns keep one CTA per tile
+    # ... a single 128-row tile per column too while its tiles fit one wave of pairs (they can
+    # then be shared along K); with more tiles than pairs it keeps one CTA per tile
     info = tv.ops.plan(R.BFLOAT16, R.BFLOAT16, 1, 128, 1024, 1024)
+    assert (info.algo, info.tile_m, info.tile_n, info.tile_k) == (TCGEN05, 256, 256, 128)
+    info = tv.ops.plan(R.BFLOAT16, R.BFLOAT16, 1, 100, 1024, 30000)
     assert (info.algo, info.tile_m, info.tile_n, info.tile_k) == (TCGEN05, 128, 256, 64)
+    # problems of at most 128 columns keep one CTA per tile
     info = tv.ops.plan(R.BFLOAT16, R.BFLOAT16, 1, 1024, 1024, 128)
     assert (info.algo, info.tile_m, info.tile_n, info.tile_k) == (TCGEN05, 128, 128, 64)
     info = tv.ops.plan(R.FLOAT32, R.FLOAT32, 1, 2592, 2048, 4096)
