@@ -11,6 +11,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <unistd.h>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -132,6 +133,36 @@ size_t dtype_size(int d) {
   static const size_t s[8] = {1, 2, 4, 8, 2, 2, 4, 8};
   return valid_dtype(d) ? s[d] : 0;
 }
+
+// ------------------------------------------------------------------------------------
+// tuning and test switches from the environment (TVB_*)
+// ------------------------------------------------------------------------------------
+// A call looks at up to ten switches; each getenv walks the whole environment.  An entry point
+// therefore takes one snapshot of the TVB_ entries (normally none) and the look-ups of that call
+// go to the snapshot.  Outside a snapshot `knob` is getenv.
+struct EnvSnapshot {
+  const char* items[24];
+  int n = 0;
+};
+thread_local const EnvSnapshot* t_env = nullptr;
+const char* knob(const char* name) {
+  if (!t_env) return getenv(name);
+  const size_t len = std::strlen(name);
+  for (int i = 0; i < t_env->n; ++i)
+    if (std::strncmp(t_env->items[i], name, len) == 0 && t_env->items[i][len] == '=') return t_env->items[i] + len + 1;
+  return nullptr;
+}
+struct EnvScope {
+  EnvSnapshot snap;
+  const EnvSnapshot* prev;
+  EnvScope() {
+    for (char** e = environ; e && *e; ++e)
+      if ((*e)[0] == 'T' && (*e)[1] == 'V' && (*e)[2] == 'B' && (*e)[3] == '_' && snap.n < 24) snap.items[snap.n++] = *e;
+    prev = t_env;
+    t_env = &snap;
+  }
+  ~EnvScope() { t_env = prev; }
+};
 
 // ------------------------------------------------------------------------------------
 // buffers of other GPUs mapped into this process (tvb_shared_open)
@@ -268,7 +299,7 @@ bool umma_eligible(int dta, int dtb, int64_t batch, int64_t M, int64_t K, int64_
   if (M > 0x7FFFFFFFll || N > 0x7FFFFFFFll || K > 0x7FFFFFFFll || batch > 0x7FFFFFFFll) return false;
   // Narrow outputs use 128-column tiles (less padding); everything else 256.
   p.block_n = (N <= 128) ? 128 : 256;
-  if (const char* e = getenv("TVB_BLOCK_N")) {
+  if (const char* e = knob("TVB_BLOCK_N")) {
     const int v = atoi(e);
     if (v == 128 || v == 256) p.block_n = v;
   }
@@ -285,7 +316,7 @@ bool umma_eligible(int dta, int dtb, int64_t batch, int64_t M, int64_t K, int64_
     // 100x1024x30000, one CTA per tile stays ahead: 17.5 against 20.1 us).
     const int64_t wide_tiles = batch * ((N + 255) / 256);
     p.pair = p.block_n == 256 && (M > 128 || wide_tiles <= sm_count / 2);
-    if (const char* e = getenv("TVB_CTA_PAIR")) p.pair = p.block_n == 256 && atoi(e) != 0;
+    if (const char* e = knob("TVB_CTA_PAIR")) p.pair = p.block_n == 256 && atoi(e) != 0;
     if (p.pair) {
       p.tile_m = 256;
       p.stages = kPairStages;
@@ -494,7 +525,7 @@ cudaError_t launch_split_transpose_t(const void* src, float* hi, float* lo, int6
   const bool vec = std::is_same_v<T, float> && N % 4 == 0 && K % 4 == 0 && kp == K && sk % 4 == 0 &&
                    (batch == 1 || sb % 4 == 0) && reinterpret_cast<uintptr_t>(src) % 16 == 0 &&
                    reinterpret_cast<uintptr_t>(hi) % 16 == 0 && reinterpret_cast<uintptr_t>(lo) % 16 == 0 &&
-                   (K + 127) / 128 <= 65535 && getenv("TVB_NO_VEC_SPLIT") == nullptr;
+                   (K + 127) / 128 <= 65535 && knob("TVB_NO_VEC_SPLIT") == nullptr;
   for (int64_t b0 = 0; b0 < batch; b0 += 65535) {
     const int nbz = static_cast<int>(batch - b0 < 65535 ? batch - b0 : 65535);
     if constexpr (std::is_same_v<T, float>) {
@@ -550,7 +581,7 @@ int run_umma(Context* c, const UmmaPlan& plan, int dta, int dtb, const Operand& 
   const uint32_t atom_k = static_cast<uint32_t>(128 / es);  // K elements per 128-byte swizzle atom
   // K elements per pipeline stage, and the K rows of one box of an MN-major operand
   // fp32 on CTA pairs: all three products of a K atom from one stage (A_hi, A_lo, B_hi, B_lo)
-  const bool fused3 = plan.op == OP_TF32 && plan.pair && plan.passes == 3 && getenv("TVB_NO_FUSED3") == nullptr;
+  const bool fused3 = plan.op == OP_TF32 && plan.pair && plan.passes == 3 && knob("TVB_NO_FUSED3") == nullptr;
   const uint32_t bk = plan.pair && !fused3 ? atom_k * kPairKAtoms : atom_k;
   const uint32_t chunk_n = static_cast<uint32_t>(128 / es);
   auto misaligned = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) != 0; };
@@ -562,7 +593,7 @@ int run_umma(Context* c, const UmmaPlan& plan, int dta, int dtb, const Operand& 
   // 2 GPUs, C5 row shards written into rank 0: 5.13 ms with 16-byte stores, 4.29 ms with row
   // stores, against 4.29 ms without any gather and 5.11 ms with an NCCL gather afterwards).
   bool c_remote = is_peer_mapping(C);
-  if (getenv("TVB_FORCE_ROW_STORES")) c_remote = true;   // lets a single GPU exercise that epilogue
+  if (knob("TVB_FORCE_ROW_STORES")) c_remote = true;   // lets a single GPU exercise that epilogue
 
   // What the kernel is given for one operand: where it starts, whether the contraction index
   // is its contiguous one (K-major) or the other (MN-major), the elements between consecutive
@@ -601,7 +632,7 @@ int run_umma(Context* c, const UmmaPlan& plan, int dta, int dtb, const Operand& 
     // pairs, as long as every share keeps 16 stages' worth of MMAs.
     uint32_t parts = rest > 0 ? std::min<uint32_t>(8, pairs / rest) : 1;
     while (parts > 2 && work / parts < 16) --parts;
-    if (const char* e = getenv("TVB_SPLIT_PARTS")) parts = std::min<uint32_t>(parts, static_cast<uint32_t>(std::max(1, atoi(e))));
+    if (const char* e = knob("TVB_SPLIT_PARTS")) parts = std::min<uint32_t>(parts, static_cast<uint32_t>(std::max(1, atoi(e))));
     // every share but the owner's takes a little less than kb / parts stages, so that its sums
     // are in memory when the owner's own sum is complete
     uint32_t kw;
@@ -617,7 +648,7 @@ int run_umma(Context* c, const UmmaPlan& plan, int dta, int dtb, const Operand& 
     }
     if (parts >= 2 && work >= 32 && kw >= 1 &&
         static_cast<size_t>(rest) * (parts - 1) * 16 <= static_cast<size_t>(Context::kMaxFlags) &&
-        getenv("TVB_NO_SPLIT_K") == nullptr) {
+        knob("TVB_NO_SPLIT_K") == nullptr) {
       sk_rest = rest;
       sk_kw = kw;
       sk_parts = parts;
@@ -754,7 +785,7 @@ int run_umma(Context* c, const UmmaPlan& plan, int dta, int dtb, const Operand& 
   p.fused3 = fused3 ? 1 : 0;
   // fp32: 256 elements of K per TMEM-resident partial sum (TVB_K_CHUNK, in stages, overrides)
   p.k_chunk_blocks = static_cast<int32_t>(256 / bk);
-  if (const char* e = getenv("TVB_K_CHUNK")) {
+  if (const char* e = knob("TVB_K_CHUNK")) {
     const int v = atoi(e);
     if (v >= 1 && v <= 4096) p.k_chunk_blocks = v;
   }
@@ -763,7 +794,7 @@ int run_umma(Context* c, const UmmaPlan& plan, int dta, int dtb, const Operand& 
   // configurations (C4 0.3245 -> 0.3139 ms and C5 9.39 -> 9.28 ms against 8; 32 is slower on both;
   // no difference where both operands fit in L2).  B is streamed from DRAM once per group.
   p.group = 16;
-  if (const char* e = getenv("TVB_TILE_GROUP")) {
+  if (const char* e = knob("TVB_TILE_GROUP")) {
     const int v = atoi(e);
     if (v >= 1 && v <= 4096) p.group = static_cast<uint32_t>(v);
   }
@@ -837,6 +868,7 @@ int matmul_views(int device, const Operand& a, const Operand& b, void* C, int dt
                  int64_t batch, int64_t M, int64_t K, int64_t N, void* stream, int algo) {
   const void* A = a.ptr;
   const void* B = b.ptr;
+  EnvScope env;
   Context* c = nullptr;
   int rc = get_ctx(device, &c);
   if (rc != TVB_OK) return rc;
@@ -1006,7 +1038,7 @@ int copy_box(Context* c, const void* src, void* dst, size_t es, const LayoutDim*
         if (i != plan.unit_dim && plan.dim[i].sstride % per16 != 0) vecs = false;
         if (i != plan.ndim - 1 && plan.dim[i].dstride % per16 != 0) vecs = false;
       }
-      if (getenv("TVB_NO_VEC_TRANSPOSE")) vecs = false;
+      if (knob("TVB_NO_VEC_TRANSPOSE")) vecs = false;
       switch (es) {
         case 1: e = vecs ? launch_tiled_transpose<uint8_t, 64, 4, true>(src, dst, plan, s)
                   : words ? launch_tiled_transpose<uint8_t, 64, 4>(src, dst, plan, s)
@@ -1557,7 +1589,7 @@ int tvb_matmul_host(int device, const void* hA, const void* hB, void* hC, int dt
   // short enough that the first product starts early (measured best on 4096^3: 4 slabs)
   int nslabs = static_cast<int>(std::min<int64_t>(Context::kMaxSlabs, batch > 1 ? batch : std::max<int64_t>(1, M / 1024)));
   if (ba + bc < (size_t(8) << 20)) nslabs = 1;            // too small to be worth cutting
-  if (const char* e = getenv("TVB_HOST_SLABS")) {
+  if (const char* e = knob("TVB_HOST_SLABS")) {
     const int v = atoi(e);
     if (v >= 1 && v <= Context::kMaxSlabs) nslabs = std::min<int>(v, static_cast<int>((units + granule - 1) / granule));
   }
