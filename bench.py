@@ -550,6 +550,14 @@ LAYOUT_TEXT = {
 }
 
 
+# (dram read + write) / algorithmic bytes of one launch, from the ncu captures of the [8192,8192]
+# cases in profiles/tiled_transpose_vec_bf16_8192x8192.md; traffic grows in proportion to the tensor.
+# Reads equal the source bytes in every capture; the ratio is below 1 because part of the result
+# was still in the L2 when the captured (single, cold) launch ended.
+NCU_LAYOUT_TRAFFIC_RATIO = {"transpose": 217.1 / 268.4, "permute": 211.4 / 268.4, "slice": 86.4 / 134.2,
+                            "concat": 49.8 / 89.7, "typecast": 348.0 / 402.7}
+
+
 def layout_arm(args):
     """One step = one layout operation over tensors resident in HBM; the metric is the algorithmic
     traffic (every element read once and written once) per second.  Single GPU."""
@@ -663,7 +671,9 @@ def layout_arm(args):
         "config": {"workload": LAYOUT_TEXT[op] + " " + shape_txt, "op": op, "elem_bytes": es,
                    "l2": f"{nsets} rotating source/destination sets exceed the {L2_BYTES >> 20} MiB L2"},
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
-                     "traffic": None, "peak_source": f"{peaks['source']}: hbm_gbs", "bytes_per_launch": bytes_algo},
+                     "traffic": NCU_LAYOUT_TRAFFIC_RATIO[op] * bytes_algo if es == 2 else None,
+                     "traffic_note": "scaled from an ncu capture of the [8192,8192] bf16 case; reads = source bytes, part of the result still in L2 at kernel end",
+                     "peak_source": f"{peaks['source']}: hbm_gbs", "bytes_per_launch": bytes_algo},
         "e2e": {"value": bytes_algo / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": src_elems * es,
                 "d2h_bytes_per_step": dst_elems * des, "ms_per_step": e2e_ms, "steps": e2e_steps,
                 "api": "tvb_memcpy_h2d + the operation + tvb_memcpy_d2h (pinned host buffers)"},
